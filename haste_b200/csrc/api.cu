@@ -1,0 +1,187 @@
+// extern "C" entry points declared in include/haste_ffi.h: argument validation, error strings and
+// dispatch to the kernel launchers.  Nothing here throws; every failure is a status code plus a
+// thread-local message.
+#include "common.cuh"
+#include "launchers.h"
+
+#include <string.h>
+
+namespace haste {
+
+static thread_local char g_err[512] = "no error";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return HASTE_OK;
+}
+int validate_shape(const char* who, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G) {
+  if (B < 1 || D < 1 || L < 1) return fail(HASTE_ERR_BAD_ARG, "%s: B=%lld D=%lld L=%lld must be positive", who, (long long)B, (long long)D, (long long)L);
+  if (!(G == 16 || G == 32 || G == 64 || G == 128)) return fail(HASTE_ERR_UNSUPPORTED, "%s: group size %lld not in {16,32,64,128}", who, (long long)G);
+  if (F < 16 || F > 128 || (F % 16) != 0) return fail(HASTE_ERR_UNSUPPORTED, "%s: fan_in %lld must be a multiple of 16 in [16,128]", who, (long long)F);
+  if (B >= (1ll << 24)) return fail(HASTE_ERR_UNSUPPORTED, "%s: batch %lld too large (< 2^24)", who, (long long)B);
+  if (D >= (1ll << 31) || (L + G - 1) / G >= (1ll << 31)) return fail(HASTE_ERR_UNSUPPORTED, "%s: D or group count exceeds int32", who);
+  return HASTE_OK;
+}
+
+}  // namespace haste
+
+using namespace haste;
+
+#define REQUIRE_PTR(p, who) \
+  if ((p) == nullptr) return fail(HASTE_ERR_BAD_ARG, "%s: argument '%s' is NULL", who, #p)
+#define REQUIRE_ALIGNED(p, who) \
+  if (!aligned16(p)) return fail(HASTE_ERR_BAD_ARG, "%s: argument '%s' must be 16-byte aligned", who, #p)
+
+extern "C" {
+
+const char* haste_last_error_string(void) { return g_err; }
+int haste_version(void) { return 100; }
+
+int haste_ffi_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
+                      int64_t L, int64_t G, int64_t ldz, haste_stream_t stream) {
+  const char* who = "haste_ffi_forward";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(z, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (ldz < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldz=%lld < L=%lld", who, (long long)ldz, (long long)L);
+  return launch_forward(loc, xt, w, bias, z, B, D, F, L, G, ldz, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_backward_features(const void* w, const int32_t* loc, const void* dy, float* dxt, int64_t B, int64_t D, int64_t F, int64_t L,
+                                int64_t G, int64_t ldy, uint32_t flags, haste_stream_t stream) {
+  const char* who = "haste_ffi_backward_features";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(w, who); REQUIRE_PTR(dy, who); REQUIRE_PTR(dxt, who);
+  REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(dxt, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (flags & HASTE_F_ZERO_DXT) {
+    cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
+    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
+  }
+  return launch_bwd_features(w, loc, dy, dxt, B, D, F, L, G, ldy, st);
+}
+
+int haste_ffi_backward_weights(const void* xt, const int32_t* loc, const void* dy, void* dw, void* dbias, int64_t B, int64_t D, int64_t F,
+                               int64_t L, int64_t G, int64_t ldy, haste_stream_t stream) {
+  const char* who = "haste_ffi_backward_weights";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(dy, who); REQUIRE_PTR(dw, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(dw, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
+  return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, void* w, void* bias, float* mom_w, float* mom_b, int64_t B,
+                         int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, int64_t label0, float lr, float wd, float mu,
+                         uint64_t seed, uint32_t step, uint32_t flags, haste_stream_t stream) {
+  const char* who = "haste_ffi_bww_sr_sgd";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(dy, who); REQUIRE_PTR(w, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who);
+  if (mom_w) REQUIRE_ALIGNED(mom_w, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
+  UpdateArgs u;
+  u.w = static_cast<__nv_bfloat16*>(w); u.bias = static_cast<__nv_bfloat16*>(bias);
+  u.mom_w = (mu != 0.f) ? mom_w : nullptr; u.mom_b = (mu != 0.f) ? mom_b : nullptr;
+  u.lr = lr; u.wd = wd; u.mu = mu; u.seed = seed; u.step = step; u.flags = flags; u.label0 = label0;
+  return launch_bwd_weights(xt, loc, dy, nullptr, nullptr, &u, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
+}
+
+int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G, int32_t* tgt_ptr, uint32_t* tgt_ent,
+                         int32_t* scratch, haste_stream_t stream) {
+  const char* who = "haste_targets_bucket";
+  if (nnz < 0 || L < 1 || G < 1 || G > 256) return fail(HASTE_ERR_BAD_ARG, "%s: bad sizes nnz=%lld L=%lld G=%lld", who, (long long)nnz, (long long)L, (long long)G);
+  if (nnz > 0) { REQUIRE_PTR(coo, who); REQUIRE_PTR(tgt_ent, who); }
+  REQUIRE_PTR(tgt_ptr, who); REQUIRE_PTR(scratch, who);
+  return launch_targets_bucket(coo, nnz, label0, L, G, tgt_ptr, tgt_ent, scratch, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
+                         const uint32_t* tgt_ent, float* dxt, float* loss, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G,
+                         int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step,
+                         uint32_t flags, haste_stream_t stream) {
+  const char* who = "haste_ffi_train_step";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(tgt_ptr, who); REQUIRE_PTR(dxt, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(dxt, who);
+  if (mom_w) REQUIRE_ALIGNED(mom_w, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (loss_kind != HASTE_LOSS_BCE && loss_kind != HASTE_LOSS_SQHINGE) return fail(HASTE_ERR_BAD_ARG, "%s: unknown loss_kind %d", who, loss_kind);
+  if ((flags & HASTE_F_LOSS) && loss == nullptr) return fail(HASTE_ERR_BAD_ARG, "%s: HASTE_F_LOSS needs a loss pointer", who);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (flags & HASTE_F_ZERO_DXT) {
+    cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
+    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
+  }
+  UpdateArgs u;
+  u.w = static_cast<__nv_bfloat16*>(w); u.bias = static_cast<__nv_bfloat16*>(bias);
+  u.mom_w = (mu != 0.f) ? mom_w : nullptr; u.mom_b = (mu != 0.f) ? mom_b : nullptr;
+  u.lr = lr; u.wd = wd; u.mu = mu; u.seed = seed; u.step = step; u.flags = flags; u.label0 = label0;
+  return launch_train_step(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);
+}
+
+int haste_sr_round(const float* x, void* out, int64_t n, uint64_t seed, haste_stream_t stream) {
+  const char* who = "haste_sr_round";
+  if (n < 0) return fail(HASTE_ERR_BAD_ARG, "%s: n < 0", who);
+  if (n > 0) { REQUIRE_PTR(x, who); REQUIRE_PTR(out, who); }
+  if (n >= (1ll << 31)) return fail(HASTE_ERR_UNSUPPORTED, "%s: the reference stream uses int32 offsets; n=%lld too large", who, (long long)n);
+  return launch_sr_round(x, out, n, seed, static_cast<cudaStream_t>(stream));
+}
+
+int haste_sgd_sr_update(void* w, const void* grad, float* mom, int64_t rows, int64_t cols, int64_t row0, float lr, float wd, float mu,
+                        uint64_t seed, uint32_t step, uint32_t flags, haste_stream_t stream) {
+  const char* who = "haste_sgd_sr_update";
+  if (rows < 0 || cols < 1) return fail(HASTE_ERR_BAD_ARG, "%s: bad shape [%lld,%lld]", who, (long long)rows, (long long)cols);
+  if (rows > 0) { REQUIRE_PTR(w, who); REQUIRE_PTR(grad, who); }
+  return launch_sgd_sr(w, grad, (mu != 0.f) ? mom : nullptr, rows, cols, row0, lr, wd, mu, seed, step, flags, static_cast<cudaStream_t>(stream));
+}
+
+int haste_dxt_to_dx_sr(const float* dxt, void* dx, int64_t B, int64_t D, uint64_t seed, haste_stream_t stream) {
+  const char* who = "haste_dxt_to_dx_sr";
+  REQUIRE_PTR(dxt, who); REQUIRE_PTR(dx, who);
+  if (B < 1 || D < 1) return fail(HASTE_ERR_BAD_ARG, "%s: bad shape", who);
+  return launch_dxt_to_dx(dxt, dx, B, D, seed, static_cast<cudaStream_t>(stream));
+}
+
+int haste_transpose_bf16(const void* x, void* xt, int64_t B, int64_t D, haste_stream_t stream) {
+  const char* who = "haste_transpose_bf16";
+  REQUIRE_PTR(x, who); REQUIRE_PTR(xt, who);
+  if (B < 1 || D < 1) return fail(HASTE_ERR_BAD_ARG, "%s: bad shape", who);
+  return launch_transpose(x, xt, B, D, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_rewire(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int32_t prune_mode,
+                     float threshold, int32_t n_prune, int32_t regrow_mode, int32_t init_mode, int32_t regroup, uint64_t seed,
+                     uint32_t step, int32_t* changed, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire";
+  REQUIRE_PTR(w, who); REQUIRE_PTR(loc, who); REQUIRE_ALIGNED(w, who);
+  if (int rc = validate_shape(who, 1, D, F, L, G)) return rc;
+  if (prune_mode < 0 || prune_mode > 1 || regrow_mode < 0 || regrow_mode > 1 || init_mode < 0 || init_mode > 1)
+    return fail(HASTE_ERR_BAD_ARG, "%s: bad mode", who);
+  if (n_prune < 0 || n_prune > F) return fail(HASTE_ERR_BAD_ARG, "%s: n_prune=%d outside [0,F]", who, n_prune);
+  if (regrow_mode == 1 && D < 2 * F) return fail(HASTE_ERR_UNSUPPORTED, "%s: 'unused' regrow needs D >= 2*F", who);
+  return launch_rewire(w, loc, mom_w, D, F, L, G, group0, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step,
+                       changed, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream) {
+  const char* who = "haste_ffi_check_locations";
+  REQUIRE_PTR(loc, who);
+  return launch_check_loc(loc, n, D, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

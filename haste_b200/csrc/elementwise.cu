@@ -1,0 +1,241 @@
+// Streaming kernels of the FFI path: stochastic rounding, the SGD(+wd)(+momentum)+SR update on a
+// stand-alone gradient tensor, the dX transpose+round tail, the bf16 transpose of the features and the
+// COO target bucketing.  All are HBM-bound: 16-byte accesses, grid sized to a multiple of the SM count.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace haste {
+
+static int grid_for(int64_t work_items, int threads) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t blocks = (work_items + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sms) * 16;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+// ---------------------------------------------------------------- fp32 -> bf16 stochastic rounding
+__global__ void __launch_bounds__(256) sr_round_kernel(const float* __restrict__ x, uint16_t* __restrict__ out, int64_t n, uint64_t seed) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = sr_bf16_bits(x[i], rand16_reference(seed, i));
+}
+
+// ---------------------------------------------------------------- SGD + SR on [rows, cols]
+// One thread owns 8 consecutive columns of one row when cols % 8 == 0 (one Philox call in the packed
+// stream, one 16-byte weight access), else one element.
+__global__ void __launch_bounds__(256) sgd_sr_vec8_kernel(uint16_t* __restrict__ w, const uint16_t* __restrict__ g, float* __restrict__ m,
+                                                          int64_t rows, int cols, int64_t row0, float lr, float wd, float mu,
+                                                          uint64_t seed, uint32_t step, uint32_t flags) {
+  const int c8n = cols >> 3;
+  const int64_t n8 = rows * c8n;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const int64_t r = i / c8n;
+    const int c8 = static_cast<int>(i - r * c8n);
+    const int64_t off = r * cols + c8 * 8;
+    uint4 wv = *reinterpret_cast<const uint4*>(w + off);
+    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(g + off));
+    uint32_t* wp = reinterpret_cast<uint32_t*>(&wv);
+    const uint32_t* gp = reinterpret_cast<const uint32_t*>(&gv);
+    float mv[8];
+    if (m) {
+      const float4 a = *reinterpret_cast<const float4*>(m + off), b = *reinterpret_cast<const float4*>(m + off + 4);
+      mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
+    }
+    uint4 rp = make_uint4(0, 0, 0, 0);
+    const bool sr = flags & HASTE_F_SR, packed = flags & HASTE_F_RNG_PACKED;
+    if (sr && packed) rp = rand_packed8(seed, step, row0 + r, c8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t r16 = 0;
+      if (sr) r16 = packed ? unpack16(rp, j) : rand16_reference(seed, (row0 + r) * cols + c8 * 8 + j);
+      const uint16_t wb = (wp[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+      const uint16_t gb = (gp[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+      const uint16_t nb = sgd_update_bits(wb, bf16_bits_to_float(gb), m ? &mv[j] : nullptr, lr, wd, mu, flags, r16);
+      wp[j >> 1] = (j & 1) ? ((wp[j >> 1] & 0xFFFFu) | (uint32_t(nb) << 16)) : ((wp[j >> 1] & 0xFFFF0000u) | nb);
+    }
+    *reinterpret_cast<uint4*>(w + off) = wv;
+    if (m) {
+      *reinterpret_cast<float4*>(m + off) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      *reinterpret_cast<float4*>(m + off + 4) = make_float4(mv[4], mv[5], mv[6], mv[7]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) sgd_sr_scalar_kernel(uint16_t* __restrict__ w, const uint16_t* __restrict__ g, float* __restrict__ m,
+                                                            int64_t rows, int cols, int64_t row0, float lr, float wd, float mu,
+                                                            uint64_t seed, uint32_t step, uint32_t flags) {
+  const int64_t n = rows * cols;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t r = i / cols;
+    const int c = static_cast<int>(i - r * cols);
+    uint32_t r16 = 0;
+    if (flags & HASTE_F_SR) r16 = rand16(flags, seed, step, row0 + r, c, cols);
+    float mv = m ? m[i] : 0.f;
+    w[i] = sgd_update_bits(w[i], bf16_bits_to_float(g[i]), m ? &mv : nullptr, lr, wd, mu, flags, r16);
+    if (m) m[i] = mv;
+  }
+}
+
+// ---------------------------------------------------------------- dxt [D,B] fp32 -> dx [B,D] bf16 (SR)
+__global__ void __launch_bounds__(256) dxt_to_dx_sr_kernel(const float* __restrict__ dxt, uint16_t* __restrict__ dx, int64_t B, int64_t D,
+                                                           uint64_t seed) {
+  __shared__ float tile[32][33];
+  const int64_t d0 = static_cast<int64_t>(blockIdx.x) * 32, b0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t d = d0 + j, b = b0 + tx;
+    tile[j][tx] = (d < D && b < B) ? dxt[d * B + b] : 0.f;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t b = b0 + j, d = d0 + tx;
+    if (b < B && d < D) {
+      const int64_t flat = b * D + d;
+      dx[flat] = sr_bf16_bits(tile[tx][j], rand16_reference(seed, flat));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, int64_t B, int64_t D) {
+  __shared__ uint16_t tile[32][34];
+  const int64_t d0 = static_cast<int64_t>(blockIdx.x) * 32, b0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t b = b0 + j, d = d0 + tx;
+    tile[j][tx] = (b < B && d < D) ? x[b * D + d] : uint16_t(0);
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t d = d0 + j, b = b0 + tx;
+    if (d < D && b < B) xt[d * B + b] = tile[tx][j];
+  }
+}
+
+// ---------------------------------------------------------------- target bucketing (COO -> per-group CSR)
+// Pass 1 counts entries per group, pass 2 turns counts into offsets (single CTA scan) and resets the
+// counters to serve as fill cursors, pass 3 scatters.  Entry order inside a group is not defined
+// (the consumers only set bits).
+__global__ void tgt_count_kernel(const int32_t* __restrict__ coo, int64_t nnz, int64_t label0, int64_t L, int G, int32_t* __restrict__ cnt) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nnz; i += stride) {
+    const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
+    if (c >= 0 && c < L) atomicAdd(&cnt[c / G], 1);
+  }
+}
+__global__ void __launch_bounds__(1024) tgt_scan_kernel(int32_t* __restrict__ cnt, int32_t* __restrict__ ptr, int64_t NG) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  for (int64_t base = 0; base < NG; base += 1024) {
+    const int64_t i = base + threadIdx.x;
+    const int v = i < NG ? cnt[i] : 0;
+    int s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    if (lane == 31) warp_sums[wid] = s;
+    __syncthreads();
+    if (wid == 0) {
+      int ws = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, ws, o);
+        if (lane >= o) ws += t;
+      }
+      warp_sums[lane] = ws;
+    }
+    __syncthreads();
+    const int excl = carry + (wid ? warp_sums[wid - 1] : 0) + s - v;
+    if (i < NG) { ptr[i] = excl; cnt[i] = 0; }
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = excl + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ptr[NG] = carry;
+}
+__global__ void tgt_fill_kernel(const int32_t* __restrict__ coo, int64_t nnz, int64_t label0, int64_t L, int G,
+                                const int32_t* __restrict__ ptr, int32_t* __restrict__ cur, uint32_t* __restrict__ ent) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nnz; i += stride) {
+    const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
+    if (c >= 0 && c < L) {
+      const int64_t g = c / G;
+      const int pos = ptr[g] + atomicAdd(&cur[g], 1);
+      ent[pos] = (static_cast<uint32_t>(coo[2 * i]) << 8) | static_cast<uint32_t>(c - g * G);
+    }
+  }
+}
+
+__global__ void check_loc_kernel(const int32_t* __restrict__ loc, int64_t n, int D, int* __restrict__ bad) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    if (loc[i] < 0 || loc[i] >= D) atomicAdd(bad, 1);
+}
+
+// ================================================================ launchers
+int launch_sr_round(const float* x, void* out, int64_t n, uint64_t seed, cudaStream_t st) {
+  if (n == 0) return HASTE_OK;
+  sr_round_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, (uint16_t*)out, n, seed);
+  return check_launch("sr_round_kernel");
+}
+
+int launch_sgd_sr(void* w, const void* g, float* m, int64_t rows, int64_t cols, int64_t row0, float lr, float wd, float mu,
+                  uint64_t seed, uint32_t step, uint32_t flags, cudaStream_t st) {
+  if (rows * cols == 0) return HASTE_OK;
+  const bool vec = (cols % 8 == 0) && aligned16(w) && aligned16(g) && (m == nullptr || aligned16(m));
+  if (vec)
+    sgd_sr_vec8_kernel<<<grid_for(rows * cols / 8, 256), 256, 0, st>>>((uint16_t*)w, (const uint16_t*)g, m, rows, int(cols), row0, lr, wd,
+                                                                       mu, seed, step, flags);
+  else
+    sgd_sr_scalar_kernel<<<grid_for(rows * cols, 256), 256, 0, st>>>((uint16_t*)w, (const uint16_t*)g, m, rows, int(cols), row0, lr, wd,
+                                                                     mu, seed, step, flags);
+  return check_launch("sgd_sr_kernel");
+}
+
+int launch_dxt_to_dx(const float* dxt, void* dx, int64_t B, int64_t D, uint64_t seed, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>((D + 31) / 32), static_cast<unsigned>((B + 31) / 32));
+  dxt_to_dx_sr_kernel<<<grid, 256, 0, st>>>(dxt, (uint16_t*)dx, B, D, seed);
+  return check_launch("dxt_to_dx_sr_kernel");
+}
+
+int launch_transpose(const void* x, void* xt, int64_t B, int64_t D, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>((D + 31) / 32), static_cast<unsigned>((B + 31) / 32));
+  transpose_bf16_kernel<<<grid, 256, 0, st>>>((const uint16_t*)x, (uint16_t*)xt, B, D);
+  return check_launch("transpose_bf16_kernel");
+}
+
+int launch_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G, int32_t* ptr, uint32_t* ent,
+                          int32_t* scratch, cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int32_t) * NG, st);
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  if (nnz > 0) tgt_count_kernel<<<grid_for(nnz, 256), 256, 0, st>>>(coo, nnz, label0, L, int(G), scratch);
+  tgt_scan_kernel<<<1, 1024, 0, st>>>(scratch, ptr, NG);
+  if (nnz > 0) tgt_fill_kernel<<<grid_for(nnz, 256), 256, 0, st>>>(coo, nnz, label0, L, int(G), ptr, scratch, ent);
+  return check_launch("targets_bucket");
+}
+
+int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st) {
+  int* bad = nullptr;
+  cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&bad), sizeof(int), st);
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMallocAsync: %s", cudaGetErrorString(e));
+  cudaMemsetAsync(bad, 0, sizeof(int), st);
+  check_loc_kernel<<<grid_for(n, 256), 256, 0, st>>>(loc, n, int(D), bad);
+  int h = 0;
+  cudaMemcpyAsync(&h, bad, sizeof(int), cudaMemcpyDeviceToHost, st);
+  cudaFreeAsync(bad, st);
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "check_locations: %s", cudaGetErrorString(e));
+  if (h != 0) return fail(HASTE_ERR_INDEX_RANGE, "%d index values outside [0,%lld)", h, (long long)D);
+  return HASTE_OK;
+}
+
+}  // namespace haste

@@ -1,0 +1,45 @@
+// Host-side launcher declarations shared between the kernel translation units and api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace haste {
+
+// Everything the fused weight/bias update needs.  mom_* are NULL when momentum is off.
+struct UpdateArgs {
+  __nv_bfloat16* w;
+  __nv_bfloat16* bias;
+  float* mom_w;
+  float* mom_b;
+  float lr, wd, mu;
+  uint64_t seed;
+  uint32_t step, flags;
+  int64_t label0;   // global index of the shard's first label (random-bit counters are global)
+};
+
+int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
+                   int64_t L, int64_t G, int64_t ldz, cudaStream_t st);
+int launch_bwd_features(const void* w, const int32_t* loc, const void* dy, float* dxt, int64_t B, int64_t D, int64_t F, int64_t L,
+                        int64_t G, int64_t ldy, cudaStream_t st);
+int launch_bwd_weights(const void* xt, const int32_t* loc, const void* dy, void* dw, void* dbias, const UpdateArgs* upd, int64_t B,
+                       int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st);
+int launch_train_step_mma(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
+                          const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
+                          cudaStream_t st);
+int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
+                      const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
+                      cudaStream_t st);
+int launch_sr_round(const float* x, void* out, int64_t n, uint64_t seed, cudaStream_t st);
+int launch_sgd_sr(void* w, const void* g, float* m, int64_t rows, int64_t cols, int64_t row0, float lr, float wd, float mu, uint64_t seed,
+                  uint32_t step, uint32_t flags, cudaStream_t st);
+int launch_dxt_to_dx(const float* dxt, void* dx, int64_t B, int64_t D, uint64_t seed, cudaStream_t st);
+int launch_transpose(const void* x, void* xt, int64_t B, int64_t D, cudaStream_t st);
+int launch_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G, int32_t* ptr, uint32_t* ent,
+                          int32_t* scratch, cudaStream_t st);
+int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st);
+int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int prune_mode,
+                  float threshold, int n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,
+                  int32_t* changed, cudaStream_t st);
+
+}  // namespace haste

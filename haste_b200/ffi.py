@@ -1,0 +1,165 @@
+"""Tensor-level wrappers over the C ABI: extract pointers, sizes and the current stream, nothing else.
+
+PyTorch is used for device memory and streams only.  Every function validates what the C side cannot
+see (device, dtype, contiguity) and raises RuntimeError otherwise.
+"""
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _req(t, name, dtype=None, contiguous=True):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return t
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def make_flags(sr=True, contract=True, rng="reference", zero_dxt=False, loss=False):
+    if rng not in ("reference", "packed"):
+        raise ValueError("rng must be 'reference' or 'packed'")
+    return ((_lib.F_SR if sr else 0) | (_lib.F_CONTRACT if contract else 0) | (_lib.F_RNG_PACKED if rng == "packed" else 0)
+            | (_lib.F_ZERO_DXT if zero_dxt else 0) | (_lib.F_LOSS if loss else 0))
+
+
+def transpose_bf16(x):
+    _req(x, "x", torch.bfloat16)
+    B, D = x.shape
+    xt = torch.empty(D, B, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.haste_transpose_bf16(_ptr(x), _ptr(xt), B, D, _stream(x)), "transpose_bf16")
+    return xt
+
+
+def forward(loc, xt, w, bias, G):
+    """z [B, L] (a view of a [B, ceil8(L)] buffer, like the reference's narrow())."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    if bias is not None:
+        _req(bias, "bias", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    ldz = (L + 7) // 8 * 8
+    z = torch.empty(B, ldz, dtype=torch.bfloat16, device=xt.device)
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_forward(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), _ptr(z), B, D, F, L, G, ldz, _stream(xt)),
+              "ffi_forward")
+    return z.narrow(1, 0, L)
+
+
+def _rows(dy, L):
+    _req(dy, "grad_outputs", torch.bfloat16, contiguous=False)
+    if dy.dim() != 2 or dy.shape[1] != L:
+        raise RuntimeError(f"grad_outputs must be [B,{L}]")
+    if dy.stride(1) != 1:
+        dy = dy.contiguous()
+    return dy, dy.stride(0)
+
+
+def backward_features(xt, w, loc, dy, G):
+    """dxt fp32 [D,B]."""
+    _req(loc, "locations", torch.int32); _req(w, "weights", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    dy, ldy = _rows(dy, L)
+    dxt = torch.empty(D, B, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(lib.haste_ffi_backward_features(_ptr(w), _ptr(loc), _ptr(dy), _ptr(dxt), B, D, F, L, G, ldy, _lib.F_ZERO_DXT,
+                                              _stream(w)), "ffi_backward_features")
+    return dxt
+
+
+def backward_weights(xt, w, loc, dy, G, want_dbias=False):
+    """dw bf16 [L,F] (and dbias bf16 [L] when asked)."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    dy, ldy = _rows(dy, L)
+    dw = torch.empty(L, F, dtype=torch.bfloat16, device=xt.device)
+    db = torch.empty(L, dtype=torch.bfloat16, device=xt.device) if want_dbias else None
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_backward_weights(_ptr(xt), _ptr(loc), _ptr(dy), _ptr(dw), _ptr(db), B, D, F, L, G, ldy, _stream(xt)),
+              "ffi_backward_weights")
+    return (dw, db) if want_dbias else dw
+
+
+def bww_sr_sgd(xt, loc, dy, w, bias, mom_w, mom_b, G, label0, lr, wd, mu, seed, step, flags):
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    dy, ldy = _rows(dy, L)
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_bww_sr_sgd(_ptr(xt), _ptr(loc), _ptr(dy), _ptr(w), _ptr(bias), _ptr(mom_w), _ptr(mom_b), B, D, F, L, G,
+                                       ldy, label0, lr, wd, mu, seed, step, flags, _stream(xt)), "ffi_bww_sr_sgd")
+
+
+def targets_bucket(coo, label0, L, G, tgt_ptr, tgt_ent, scratch):
+    _req(coo, "targets", torch.int32)
+    nnz = coo.shape[0]
+    NG = (L + G - 1) // G
+    if tgt_ptr.numel() < NG + 1 or scratch.numel() < NG or tgt_ent.numel() < nnz:
+        raise RuntimeError("targets_bucket: output buffers too small")
+    with torch.cuda.device(coo.device):
+        check(lib.haste_targets_bucket(_ptr(coo), nnz, label0, L, G, _ptr(tgt_ptr), _ptr(tgt_ent), _ptr(scratch), _stream(coo)),
+              "targets_bucket")
+
+
+def train_step(loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, mu,
+               seed, step, flags):
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    _req(dxt, "dxt", torch.float32)
+    D, B = xt.shape
+    L, F = w.shape
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_train_step(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), _ptr(mom_w), _ptr(mom_b), _ptr(tgt_ptr),
+                                       _ptr(tgt_ent), _ptr(dxt), _ptr(loss), B, D, F, L, G, label0, loss_kind, grad_scale, lr, wd,
+                                       mu, seed, step, flags, _stream(xt)), "ffi_train_step")
+
+
+def sr_round(x, out, seed):
+    _req(x, "x", torch.float32); _req(out, "output", torch.bfloat16)
+    with torch.cuda.device(x.device):
+        check(lib.haste_sr_round(_ptr(x), _ptr(out), x.numel(), seed, _stream(x)), "sr_round")
+
+
+def sgd_sr_update(w, grad, mom, row0, lr, wd, mu, seed, step, flags):
+    _req(w, "weights", torch.bfloat16); _req(grad, "gradient", torch.bfloat16)
+    rows = w.shape[0] if w.dim() >= 1 else 1
+    cols = w.numel() // max(rows, 1) if w.dim() >= 2 else 1
+    with torch.cuda.device(w.device):
+        check(lib.haste_sgd_sr_update(_ptr(w), _ptr(grad), _ptr(mom), rows, cols, row0, lr, wd, mu, seed, step, flags, _stream(w)),
+              "sgd_sr_update")
+
+
+def dxt_to_dx_sr(dxt, seed=123):
+    _req(dxt, "dxt", torch.float32)
+    D, B = dxt.shape
+    dx = torch.empty(B, D, dtype=torch.bfloat16, device=dxt.device)
+    with torch.cuda.device(dxt.device):
+        check(lib.haste_dxt_to_dx_sr(_ptr(dxt), _ptr(dx), B, D, seed, _stream(dxt)), "dxt_to_dx_sr")
+    return dx
+
+
+def rewire(w, loc, mom_w, D, G, group0, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step, changed=None):
+    _req(w, "weights", torch.bfloat16); _req(loc, "group_locations", torch.int32)
+    L, F = w.shape
+    with torch.cuda.device(w.device):
+        check(lib.haste_ffi_rewire(_ptr(w), _ptr(loc), _ptr(mom_w), D, F, L, G, group0, prune_mode, float(threshold), int(n_prune),
+                                   regrow_mode, init_mode, int(bool(regroup)), seed, step, _ptr(changed), _stream(w)), "ffi_rewire")
+
+
+def check_locations(loc, D):
+    _req(loc, "group_locations", torch.int32)
+    with torch.cuda.device(loc.device):
+        check(lib.haste_ffi_check_locations(_ptr(loc), loc.numel(), D, _stream(loc)), "check_locations")

@@ -1,0 +1,140 @@
+"""Fused training step of the FFI layer, single shard and label-sharded across ranks.
+
+``FusedFFIShard`` owns one contiguous range of label groups (weights, bias, index table, optional
+momentum) and runs forward + loss gradient + both backwards + the SGD/stochastic-rounding update as one
+kernel launch; neither logits nor their gradient are written to memory.
+
+``ShardedFFILayer`` splits the groups of a layer contiguously over the ranks of a ``torch.distributed``
+process group (features replicated, one process per GPU) and sums the per-rank feature gradients with a
+single all-reduce — the only exchange step of the path.  Random-bit counters use global label indices, so
+the updated weights do not depend on the number of ranks.
+"""
+import torch
+
+from . import _lib
+from . import ffi as _ffi
+
+LOSSES = {"bce": _lib.LOSS_BCE, "squared_hinge": _lib.LOSS_SQHINGE}
+
+
+def shard_groups(num_groups, world_size, rank):
+    """Contiguous, near-equal split of ``num_groups`` label groups: returns [g0, g1) of ``rank``."""
+    base, rem = divmod(num_groups, world_size)
+    g0 = rank * base + min(rank, rem)
+    return g0, g0 + base + (1 if rank < rem else 0)
+
+
+def shard_labels(L, G, world_size, rank):
+    """Label range [l0, l1) and group range [g0, g1) owned by ``rank`` (whole groups only; the ragged last
+    group goes to the last non-empty shard)."""
+    NG = (L + G - 1) // G
+    g0, g1 = shard_groups(NG, world_size, rank)
+    return min(L, g0 * G), min(L, g1 * G), g0, g1
+
+
+class FusedFFIShard:
+    def __init__(self, group_locations, weights, bias, group_size, in_features, *, label0=0, loss="bce", lr=0.05,
+                 weight_decay=0.0, momentum=0.0, seed=123, rng="packed", contract=True, grad_scale=1.0,
+                 stochastic_rounding=True, max_nnz=1 << 16):
+        if loss not in LOSSES:
+            raise ValueError(f"loss must be one of {sorted(LOSSES)}")
+        dev = weights.device
+        self.loc, self.w, self.bias = group_locations, weights, bias
+        self.G, self.D, self.label0 = int(group_size), int(in_features), int(label0)
+        self.L, self.F = weights.shape
+        self.NG = (self.L + self.G - 1) // self.G
+        self.loss_kind, self.grad_scale = LOSSES[loss], float(grad_scale)
+        self.lr, self.wd, self.mu, self.seed = float(lr), float(weight_decay), float(momentum), int(seed)
+        self.rng, self.contract, self.sr = rng, bool(contract), bool(stochastic_rounding)
+        self.steps = 0
+        self.mom_w = torch.zeros_like(weights, dtype=torch.float32) if self.mu != 0.0 else None
+        self.mom_b = torch.zeros_like(bias, dtype=torch.float32) if (self.mu != 0.0 and bias is not None) else None
+        self.tgt_ptr = torch.zeros(self.NG + 1, dtype=torch.int32, device=dev)
+        self.tgt_ent = torch.zeros(max_nnz, dtype=torch.int32, device=dev)
+        self.scratch = torch.zeros(self.NG, dtype=torch.int32, device=dev)
+        self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._dxt = None
+
+    def _keys(self):
+        # reference stream: the optimizer's seed advances by one per step (optim_sr.py:59-62);
+        # packed stream: key (seed, step)
+        if self.rng == "reference":
+            return self.seed + self.steps, 0
+        return self.seed, self.steps
+
+    def bucket_targets(self, targets):
+        """``targets``: int32 [nnz,2] (row, GLOBAL label id) on the device.  Entries outside this shard are dropped."""
+        if targets.shape[0] > self.tgt_ent.numel():
+            self.tgt_ent = torch.zeros(int(targets.shape[0] * 1.5) + 1, dtype=torch.int32, device=targets.device)
+        _ffi.targets_bucket(targets, self.label0, self.L, self.G, self.tgt_ptr, self.tgt_ent, self.scratch)
+
+    def step_xt(self, xt, targets, dxt=None, want_loss=True):
+        """One step given the transposed features [D,B] (bf16).  Returns (dxt fp32 [D,B], loss fp32 [1] or None)."""
+        D, B = xt.shape
+        if dxt is None:
+            if self._dxt is None or self._dxt.shape != (D, B):
+                self._dxt = torch.empty(D, B, dtype=torch.float32, device=xt.device)
+            dxt = self._dxt
+        self.bucket_targets(targets)
+        if want_loss:
+            self.loss_buf.zero_()
+        seed, step = self._keys()
+        flags = _ffi.make_flags(sr=self.sr, contract=self.contract, rng=self.rng, zero_dxt=True, loss=want_loss)
+        _ffi.train_step(self.loc, xt, self.w, self.bias, self.mom_w, self.mom_b, self.tgt_ptr, self.tgt_ent, dxt,
+                        self.loss_buf if want_loss else None, self.G, self.label0, self.loss_kind, self.grad_scale, self.lr,
+                        self.wd, self.mu, seed, step, flags)
+        self.steps += 1
+        return dxt, (self.loss_buf if want_loss else None)
+
+    def step(self, x, targets, want_loss=True):
+        """One step given features [B,D] (bf16, device)."""
+        return self.step_xt(_ffi.transpose_bf16(x), targets, want_loss=want_loss)
+
+
+class ShardedFFILayer:
+    """Label-sharded layer: this rank's ``FusedFFIShard`` plus the dX all-reduce.
+
+    ``full_*`` tensors describe the whole layer (on any device); each rank copies its slice to ``device``.
+    """
+
+    def __init__(self, full_locations, full_weights, full_bias, group_size, in_features, device, *, process_group=None,
+                 rank=None, world_size=None, **shard_kwargs):
+        import torch.distributed as dist
+        self.dist = dist
+        self.pg = process_group
+        if rank is None:
+            rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        if world_size is None:
+            world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank, self.world = rank, world_size
+        L = full_weights.shape[0]
+        l0, l1, g0, g1 = shard_labels(L, group_size, world_size, rank)
+        self.l0, self.l1, self.g0, self.g1 = l0, l1, g0, g1
+        self.shard = FusedFFIShard(full_locations[g0:g1].to(device).contiguous(), full_weights[l0:l1].to(device).contiguous(),
+                                   None if full_bias is None else full_bias[l0:l1].to(device).contiguous(), group_size,
+                                   in_features, label0=l0, **shard_kwargs)
+        self.comm_stream = torch.cuda.Stream(device=device) if (world_size > 1 and torch.device(device).type == "cuda") else None
+
+    def step(self, x, targets, want_loss=True):
+        """Returns (dxt summed over all ranks, this rank's loss part).  The all-reduce runs on a side stream;
+        the caller's stream waits for it before returning."""
+        dxt, loss = self.shard.step(x, targets, want_loss=want_loss)
+        allreduce_sum(dxt, self.pg, self.comm_stream, self.world)
+        return dxt, loss
+
+
+def allreduce_sum(t, process_group=None, comm_stream=None, world_size=None):
+    """Sum ``t`` over the ranks in place (NCCL for CUDA tensors, any backend for CPU tensors)."""
+    import torch.distributed as dist
+    if world_size is None:
+        world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+    if world_size <= 1:
+        return t
+    if comm_stream is not None:
+        comm_stream.wait_stream(torch.cuda.current_stream(t.device))
+        with torch.cuda.stream(comm_stream):
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=process_group)
+        torch.cuda.current_stream(t.device).wait_stream(comm_stream)
+    else:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=process_group)
+    return t

@@ -1,0 +1,156 @@
+/*
+ * haste_ffi.h — C ABI of the B200 (sm_100a) fixed-fan-in (FFI) output-layer kernels.
+ *
+ * This is the drop-in boundary for the training hot path of HASTE's grouped fixed-fan-in sparse
+ * output layer.  Every entry point takes raw device pointers, 64-bit sizes, scalar
+ * hyper-parameters and a CUDA stream, returns an int status (0 = ok) and never throws.
+ * After a non-zero status, haste_last_error_string() describes the failure (thread-local).
+ * The caller makes the target device current before calling; all work is enqueued on `stream`.
+ *
+ * Notation: B batch, D input features, L labels (of this shard), F fan-in, G group size,
+ * NG = ceil(L/G).  bf16 tensors are passed as `const void*` / `void*` (2 bytes per element).
+ *   loc   int32 [NG,F]   input-feature index table, one row per group of G consecutive labels
+ *   xt    bf16  [D,B]    features TRANSPOSED (batch contiguous), as the reference's kernels take them
+ *   w     bf16  [L,F]    weights
+ *   bias  bf16  [L]      optional (NULL = none)
+ *   z/dy  bf16  [B,ld]   logits / dLoss/dLogits, row stride `ld` elements (ld >= L)
+ *   dxt   fp32  [D,B]    gradient w.r.t. xt
+ *
+ * Supported shapes: G in {16,32,64,128}; F a multiple of 16, 16 <= F <= 128; B >= 1; any L >= 1.
+ * (The reference supports G in {16,32,64}: shared_ffi/rewire.py:120.)
+ */
+#ifndef HASTE_FFI_H
+#define HASTE_FFI_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* haste_stream_t; /* a cudaStream_t */
+
+enum {
+  HASTE_OK = 0,
+  HASTE_ERR_BAD_ARG = 1,     /* null pointer, negative size, misaligned base pointer */
+  HASTE_ERR_UNSUPPORTED = 2, /* (G,F) or size outside the supported set */
+  HASTE_ERR_INDEX_RANGE = 3, /* loc holds a value outside [0,D) (haste_ffi_check_locations) */
+  HASTE_ERR_LAUNCH = 4,      /* CUDA reported an error at launch */
+  HASTE_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+  HASTE_ERR_TOO_LARGE = 6    /* size beyond a documented fixed capacity */
+};
+
+/* loss_kind */
+enum { HASTE_LOSS_BCE = 0, HASTE_LOSS_SQHINGE = 1 };
+
+/* flags for the update / train-step entry points */
+enum {
+  HASTE_F_SR = 1u << 0,          /* stochastic rounding to bf16 (else round-to-nearest-even) */
+  HASTE_F_CONTRACT = 1u << 1,    /* fp32 update uses fused multiply-add, as the reference's compiled
+                                    Triton kernel does; clear = separate multiply and add */
+  HASTE_F_RNG_PACKED = 1u << 2,  /* random bits: one Philox4x32-10 call per 8 slots, key (seed,step),
+                                    counter (global label, slot>>3,0,0); clear = the reference stream
+                                    (tl.randint: key seed, counter flat element index, word 0) */
+  HASTE_F_ZERO_DXT = 1u << 3,    /* clear dxt on the stream before accumulating into it */
+  HASTE_F_LOSS = 1u << 4         /* accumulate the loss value into *loss */
+};
+
+const char* haste_last_error_string(void);
+int haste_version(void);
+
+/* Forward: z[b,l] = sum_k xt[loc[l/G,k], b] * w[l,k] + bias[l], fp32 accumulate, RN to bf16.
+ * Columns L..ldz-1 of z are written with zeros when ldz > L (the reference pads to a multiple of 8).
+ * Replaces ffi_forward_cuda (shared_ffi/ffi_forward_kernels.cu:492-719, bound at ffi_wrapper.cpp:32-44). */
+int haste_ffi_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z,
+                      int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldz,
+                      haste_stream_t stream);
+
+/* Backward w.r.t. features: dxt[loc[g,k], b] += sum_{l in g} w[l,k] * dy[b,l]  (fp32 atomics).
+ * flags: HASTE_F_ZERO_DXT clears dxt first (the reference allocates zeros).
+ * Replaces ffi_backward_features_cuda (shared_ffi/ffi_backward_features.cu:417-633). */
+int haste_ffi_backward_features(const void* w, const int32_t* loc, const void* dy, float* dxt,
+                                int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy,
+                                uint32_t flags, haste_stream_t stream);
+
+/* Backward w.r.t. weights: dw[l,k] = sum_b dy[b,l] * xt[loc[l/G,k], b], RN to bf16;
+ * dbias (optional, bf16 [L]) = column sums of dy (shared_ffi/bindings.py:39-42).
+ * Replaces ffi_backward_weights_cuda (shared_ffi/ffi_backward_weights.cu:486-684). */
+int haste_ffi_backward_weights(const void* xt, const int32_t* loc, const void* dy, void* dw, void* dbias,
+                               int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy,
+                               haste_stream_t stream);
+
+/* Backward-weights fused with the SGD(+weight decay)(+momentum) stochastic-rounding update: the
+ * gradient is rounded to bf16 exactly as haste_ffi_backward_weights would store it and consumed in
+ * registers; w (and bias, momentum buffers when given) are updated in place.
+ * label0 = global index of this shard's first label (random-bit counters use global indices).
+ * Replaces ffi_backward_weights_cuda followed by sr_triton.sgd_update
+ * (shared_ffi/sr_triton.py:172-213, called from shared_ffi/optim_sr.py:99-109). */
+int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, void* w, void* bias,
+                         float* mom_w, float* mom_b,
+                         int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, int64_t label0,
+                         float lr, float wd, float mu, uint64_t seed, uint32_t step, uint32_t flags,
+                         haste_stream_t stream);
+
+/* Bucket COO targets (row, col) int32 [nnz,2] by label group for the fused step.
+ * Keeps entries with label0 <= col < label0+L.  Outputs: tgt_ptr int32 [NG+1] (CSR offsets),
+ * tgt_ent uint32 [nnz] = (row << 8) | (col - label0) % G.  `scratch` is NG int32 of device memory.
+ * The COO layout is the reference collate's (src/data.py:26-46). */
+int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G,
+                         int32_t* tgt_ptr, uint32_t* tgt_ent, int32_t* scratch, haste_stream_t stream);
+
+/* Fused training step of the layer for one label shard:
+ *   z = forward; dy = grad_scale * dLoss/dz (BCE-with-logits sum, or squared hinge);
+ *   dxt += backward-features; w,bias <- SGD(+wd)(+momentum) + stochastic rounding of backward-weights.
+ * Neither z nor dy nor dw is written to memory.  Targets come from haste_targets_bucket.
+ * loss (optional fp32 device scalar) is accumulated into when HASTE_F_LOSS is set.
+ * Replaces GroupFFIMulFunction.forward/backward (shared_ffi/bindings.py:12-54), the loss of
+ * src/runner.py:469-494 and SRSgd.step (shared_ffi/optim_sr.py:46-114) for this layer. */
+int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias,
+                         float* mom_w, float* mom_b,
+                         const int32_t* tgt_ptr, const uint32_t* tgt_ent,
+                         float* dxt, float* loss,
+                         int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t label0,
+                         int32_t loss_kind, float grad_scale, float lr, float wd, float mu,
+                         uint64_t seed, uint32_t step, uint32_t flags, haste_stream_t stream);
+
+/* Elementwise stochastic rounding fp32 -> bf16 with the reference stream over the flat index.
+ * Replaces sr_triton.stochastic_rounding (shared_ffi/sr_triton.py:27-59). */
+int haste_sr_round(const float* x, void* out, int64_t n, uint64_t seed, haste_stream_t stream);
+
+/* Elementwise SGD(+wd)(+momentum) + SR/RN on a [rows,cols] bf16 parameter, in place.
+ * grad is bf16 [rows,cols]; mom fp32 or NULL; row0 = global index of the first row.
+ * Replaces sr_triton.sgd_update (shared_ffi/sr_triton.py:109-213). */
+int haste_sgd_sr_update(void* w, const void* grad, float* mom, int64_t rows, int64_t cols, int64_t row0,
+                        float lr, float wd, float mu, uint64_t seed, uint32_t step, uint32_t flags,
+                        haste_stream_t stream);
+
+/* dX tail of the autograd backward: transpose fp32 dxt [D,B] to [B,D] and stochastically round to
+ * bf16, counter = flat index in [B,D] (shared_ffi/bindings.py:44-50 uses the fixed seed 123). */
+int haste_dxt_to_dx_sr(const float* dxt, void* dx, int64_t B, int64_t D, uint64_t seed,
+                       haste_stream_t stream);
+
+/* Transpose bf16 x [B,D] -> xt [D,B] (shared_ffi/bindings.py:19 does this with torch). */
+int haste_transpose_bf16(const void* x, void* xt, int64_t B, int64_t D, haste_stream_t stream);
+
+/* Rewire: per-group prune of the lowest-score slots, regrow, re-initialise, regroup; in place.
+ *   score[g,k] = mean over the group's real rows of |w[l,k]| (fp32, rows summed in order)
+ *   prune_mode 0 'threshold': score < threshold; 1 'fraction': the n_prune lowest (ties: lowest slot)
+ *   regrow_mode 0 'replace' (uniform with replacement, the reference's rule), 1 'unused'
+ *   init_mode 0 'zero', 1 'random' U(+-1/sqrt(F));  regroup != 0 sorts each index row ascending and
+ *   permutes the group's weight and momentum columns with it.
+ * group0 = global index of this shard's first group (random draws use global indices).
+ * changed (optional int32 device scalar) receives the number of pruned (group,slot) pairs.
+ * Replaces the tensor math of GroupFixedFanIn.rewire (shared_ffi/rewire.py:143-239). */
+int haste_ffi_rewire(void* w, int32_t* loc, float* mom_w,
+                     int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0,
+                     int32_t prune_mode, float threshold, int32_t n_prune,
+                     int32_t regrow_mode, int32_t init_mode, int32_t regroup,
+                     uint64_t seed, uint32_t step, int32_t* changed, haste_stream_t stream);
+
+/* Debug check: every loc value in [0,D).  Synchronises the stream. */
+int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HASTE_FFI_H */

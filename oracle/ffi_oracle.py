@@ -196,10 +196,15 @@ def stochastic_rounding(x32, seed):
     return _bits_to_bf16(px.sr_bf16_bits(x, r))
 
 
-def rand16_for(shape, seed, step, mode, row0=0):
+BIAS_KEY_XOR = 0x62696173   # packed stream: 1-D parameters use seed ^ this, so bias does not reuse column 0's bits
+
+
+def rand16_for(shape, seed, step, mode, row0=0, is_bias=False):
     """Random 16-bit field for a [rows, cols] parameter.  mode 'reference': tl.randint stream over
     the flat index (row0 shifts to the global row); 'packed': one Philox call per 8 slots."""
     rows, cols = shape
+    if mode != 'reference' and is_bias:
+        seed = int(seed) ^ BIAS_KEY_XOR
     r = np.arange(rows, dtype=np.int64)[:, None] + row0
     c = np.arange(cols, dtype=np.int64)[None, :]
     if mode == 'reference':
@@ -227,7 +232,7 @@ def train_step(loc, X, W, bias, targets, G, loss_kind, lr, wd, seed, step=0, gra
     out = dict(Z=Z, dY=dY, loss=loss, dXt=dXt, dW=dW, W_new=W_new, bias_new=None)
     if bias is not None:
         db = bias_grad(dY)
-        rb = rand16_for((L, 1), seed, step, rng_mode, row0).reshape(L)
+        rb = rand16_for((L, 1), seed, step, rng_mode, row0, is_bias=True).reshape(L)
         out['bias_new'], _ = sgd_update(bias, db, None, lr, wd, 0.0, False, True, rb, contract)
         out['dbias'] = db
     return out
@@ -281,7 +286,7 @@ def regrow_init_value(seed, step, l, k, F):
 
 def rewire(W, loc, G, D, prune_mode, rewire_fraction=None, rewire_threshold=None,
            init_mode='zero', regrow='unused', regroup=True, seed=0, step=0,
-           injected=None, momentum=None):
+           injected=None, momentum=None, group0=0):
     """Prune + regrow (+ regroup).  Returns (W_new bf16, loc_new int32, momentum_new).
 
     regrow:
@@ -311,15 +316,17 @@ def rewire(W, loc, G, D, prune_mode, rewire_fraction=None, rewire_threshold=None
             if injected is not None:
                 v = int(injected[inj]); inj += 1
             elif regrow == 'replace':
-                v = regrow_index(seed, step, g, int(k), 0, D)
+                v = regrow_index(seed, step, group0 + g, int(k), 0, D)
             else:
-                t = 0
-                v = regrow_index(seed, step, g, int(k), t, D)
-                while v in used and t < 64:
-                    t += 1
-                    v = regrow_index(seed, step, g, int(k), t, D)
-                while v in used:                    # bounded fallback: next free index upward
+                found = False
+                for t in range(64):
+                    v = regrow_index(seed, step, group0 + g, int(k), t, D)
+                    if v not in used:
+                        found = True
+                        break
+                while not found:                    # bounded fallback: next free index upward
                     v = (v + 1) % D
+                    found = v not in used
                 used.add(v)
             locn[g, k] = v
         l0, l1 = g * G, min(L, (g + 1) * G)
@@ -327,7 +334,7 @@ def rewire(W, loc, G, D, prune_mode, rewire_fraction=None, rewire_threshold=None
             if init_mode == 'zero':
                 Wb[l0:l1, k] = 0
             else:
-                vals = np.array([regrow_init_value(seed, step, l, int(k), F) for l in range(l0, l1)],
+                vals = np.array([regrow_init_value(seed, step, group0 * G + l, int(k), F) for l in range(l0, l1)],
                                 np.float32)
                 Wb[l0:l1, k] = px.rn_bf16_bits(vals)
             if mom is not None:

@@ -1,0 +1,113 @@
+"""CPU-side tests: the C-ABI library loads and exports every declared symbol, the host-side sharding logic,
+and a 2-rank gloo run of the label-sharded step (the oracle stands in for the kernels on CPU)."""
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    path = os.path.join(ROOT, "haste_b200", "libhaste_ffi.so")
+    if not os.path.exists(path):
+        from haste_b200 import build
+        build.build()
+    return path
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    import ctypes
+    header = open(os.path.join(ROOT, "include", "haste_ffi.h")).read()
+    declared = set(re.findall(r"\b(haste_[a-z0-9_]+)\s*\(", header))
+    declared.discard("haste_stream_t")
+    assert len(declared) >= 12
+    lib = ctypes.CDLL(built_lib)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/haste_ffi.h but not exported"
+    from haste_b200 import _lib
+    assert set(_lib.SIGNATURES) | {"haste_last_error_string", "haste_version"} == declared
+    assert _lib.lib.haste_version() >= 100
+
+
+def test_argument_validation_without_gpu(built_lib):
+    # status codes and messages of the C ABI for calls that are rejected before any CUDA work
+    from haste_b200 import _lib
+    rc = _lib.lib.haste_ffi_forward(None, None, None, None, None, 1, 1, 16, 1, 32, 8, None)
+    assert rc == _lib.ERR_BAD_ARG and "NULL" in _lib.last_error()
+    buf = (ctypes_buf := __import__("ctypes").create_string_buffer(64))
+    addr = __import__("ctypes").addressof(buf)
+    addr += (-addr) % 16
+    rc = _lib.lib.haste_ffi_forward(addr, addr, addr, None, addr, 4, 8, 16, 10, 48, 16, None)
+    assert rc == _lib.ERR_UNSUPPORTED and "group size" in _lib.last_error()
+    rc = _lib.lib.haste_ffi_forward(addr, addr, addr, None, addr, 4, 8, 24, 10, 32, 16, None)
+    assert rc == _lib.ERR_UNSUPPORTED and "fan_in" in _lib.last_error()
+    rc = _lib.lib.haste_ffi_forward(addr, addr, addr, None, addr, 4, 8, 16, 10, 32, 8, None)
+    assert rc == _lib.ERR_BAD_ARG and "ldz" in _lib.last_error()
+    with pytest.raises(RuntimeError):
+        _lib.check(rc, "forward")
+
+
+def test_product_does_not_import_oracle():
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "haste_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", src, re.M), f"{f} imports the oracle"
+
+
+def test_shard_partition():
+    from haste_b200.fused import shard_groups, shard_labels
+    for NG in (1, 7, 8, 5236, 21971):
+        for R in (1, 2, 4, 8):
+            ranges = [shard_groups(NG, R, r) for r in range(R)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == NG
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            sizes = [b - a for a, b in ranges]
+            assert max(sizes) - min(sizes) <= 1
+    L, G = 670091, 128
+    parts = [shard_labels(L, G, 8, r) for r in range(8)]
+    assert parts[0][0] == 0 and parts[-1][1] == L and all(p[0] % G == 0 for p in parts)
+
+
+_WORKER = r"""
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from oracle import ffi_oracle as fo
+from haste_b200.fused import shard_labels, allreduce_sum
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+B, D, L, F, G = 32, 64, 700, 16, 32
+inp = fo.make_inputs(B, D, L, F, G, 5, 1.1, seed=3, bias_zero=False)
+l0, l1, g0, g1 = shard_labels(L, G, 2, rank)
+tg = inp["targets"]
+keep = (tg[:, 1] >= l0) & (tg[:, 1] < l1)
+tl = tg[keep].clone(); tl[:, 1] -= l0
+out = fo.train_step(inp["loc"][g0:g1], inp["X"], inp["W"][l0:l1], inp["bias"][l0:l1], tl, G, fo.LOSS_BCE, 0.05, 1e-4, 123,
+                    step=2, rng_mode="packed", row0=l0)
+dxt = out["dXt"].clone()
+allreduce_sum(dxt)                        # the path's only exchange step
+full = fo.train_step(inp["loc"], inp["X"], inp["W"], inp["bias"], tg, G, fo.LOSS_BCE, 0.05, 1e-4, 123, step=2, rng_mode="packed")
+assert torch.allclose(dxt, full["dXt"], atol=1e-5), "summed dX differs from the unsharded step"
+assert torch.equal(out["W_new"], full["W_new"][l0:l1]), "sharded weights differ"
+assert torch.equal(out["bias_new"], full["bias_new"][l0:l1])
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_rank_gloo_sharded_step(tmp_path, built_lib):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    port = str(29500 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+             for r in range(2)]
+    for p in procs:
+        out, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, out.decode()
