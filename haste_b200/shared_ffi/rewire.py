@@ -86,7 +86,7 @@ class GroupFixedFanIn(torch.nn.Module):
             n_prune, mode, thr = 0, 0, float(self.rewire_threshold)
         changed = torch.zeros(1, dtype=torch.int32, device=self.weights.device)
         _ffi.rewire(self.weights.data, self.group_locations, momentum_buf, self.in_features, self.group_size, 0, mode, thr,
-                    n_prune, REGROW_MODES.index(self.regrow), INIT_MODES.index(self.init_mode), self.regroup, self.seed,
+                    n_prune, {'replace': 0, 'unused': 1}[self.regrow], {'zero': 0, 'random': 1}[self.init_mode], self.regroup, self.seed,
                     self._rewire_calls, changed)
         self._rewire_calls += 1
         return int(changed.item())

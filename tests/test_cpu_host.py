@@ -40,8 +40,9 @@ def test_argument_validation_without_gpu(built_lib):
     from haste_b200 import _lib
     rc = _lib.lib.haste_ffi_forward(None, None, None, None, None, 1, 1, 16, 1, 32, 8, None)
     assert rc == _lib.ERR_BAD_ARG and "NULL" in _lib.last_error()
-    buf = (ctypes_buf := __import__("ctypes").create_string_buffer(64))
-    addr = __import__("ctypes").addressof(buf)
+    import ctypes
+    buf = ctypes.create_string_buffer(64)
+    addr = ctypes.addressof(buf)
     addr += (-addr) % 16
     rc = _lib.lib.haste_ffi_forward(addr, addr, addr, None, addr, 4, 8, 16, 10, 48, 16, None)
     assert rc == _lib.ERR_UNSUPPORTED and "group size" in _lib.last_error()

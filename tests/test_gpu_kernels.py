@@ -59,15 +59,18 @@ def _assert_close(got, want, rel=REL, abs_=ABS, what=""):
     assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} outside tolerance, max err {float(err.max())}"
 
 
-def _assert_bf16_ulp(got_bits, want_bits, max_ulp=2, max_frac=0.05, what=""):
+def _assert_bf16_ulp(got_bits, want_bits, max_ulp=2, max_frac=0.05, what="", extra_abs=0.0):
+    """Bit patterns may differ in at most ``max_frac`` of the elements, and then by at most ``max_ulp`` bf16
+    steps of the value plus ``extra_abs`` (array or scalar: the effect of a one-step difference in an input)."""
     g = px.bf16_bits_to_f32(got_bits).astype(np.float64)
     w = px.bf16_bits_to_f32(want_bits).astype(np.float64)
     neq = got_bits != want_bits
     frac = neq.mean()
     assert frac <= max_frac, f"{what}: {frac:.4f} of elements differ"
     if neq.any():
-        d = np.abs(g - w)[neq] / np.maximum(_ulp_bf16(w[neq]), 1e-30)
-        assert d.max() <= max_ulp + 1e-6, f"{what}: max diff {d.max()} ulp"
+        tol = max_ulp * _ulp_bf16(w) + extra_abs
+        over = (np.abs(g - w) - tol)[neq]
+        assert over.max() <= 1e-12, f"{what}: a difference exceeds its tolerance by {over.max()}"
 
 
 # ------------------------------------------------------------------------------------------------ GEMM phases
@@ -276,8 +279,15 @@ def test_train_step_vs_oracle(hb, shape, loss_name):
                             grad_scale=scale, rng_mode=rng)
         _assert_close(dxt, ref["dXt"], rel=1e-2, abs_=2e-3 * max(1.0, float(ref["dXt"].abs().max())), what="dXt")
         assert abs(float(loss) - ref["loss"]) <= 2e-3 * abs(ref["loss"]) + 1e-3, (float(loss), ref["loss"])
-        _assert_bf16_ulp(_bits(w), fo._bf16_to_bits(ref["W_new"]), what="W")
-        _assert_bf16_ulp(_bits(b), fo._bf16_to_bits(ref["bias_new"]), max_ulp=4, max_frac=0.2, what="bias")
+        # Not bit-exact by construction (the kernel's fp32 summation order differs from the oracle's fp64 sums, so a
+        # logit can round to the neighbouring bf16 and move one dY entry by one bf16 step): a weight may move by
+        # lr * (a few bf16 steps of dW + one bf16 step of dY times the largest |x|).  The bit-exact statement of
+        # the fused step is test_train_step_hinge_bit_exact_chain.
+        flip = 2.0 ** -7 * float(ref["dY"].float().abs().max()) * float(inp["X"].float().abs().max())
+        gw = 0.05 * (4 * _ulp_bf16(ref["dW"].float().numpy()) + flip)
+        gb = 0.05 * (4 * _ulp_bf16(ref["dbias"].float().numpy()) + 2.0 ** -7 * float(ref["dY"].float().abs().max()))
+        _assert_bf16_ulp(_bits(w), fo._bf16_to_bits(ref["W_new"]), what="W", extra_abs=gw)
+        _assert_bf16_ulp(_bits(b), fo._bf16_to_bits(ref["bias_new"]), max_ulp=2, max_frac=0.2, what="bias", extra_abs=gb)
 
 
 @pytest.mark.parametrize("shape", [(200, 256, 1111, 64, 128), (256, 512, 777, 128, 64), (64, 768, 1000, 32, 32)])
