@@ -28,6 +28,8 @@ SIGNATURES = {
     "haste_targets_bucket": [P, I64, I64, I64, I64, P, P, P, P],
     "haste_ffi_train_step": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64,
                              U32, U32, P],
+    "haste_ffi_train_step_dbg": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64,
+                                 U32, U32, P, I64, P, P, P],
     "haste_sr_round": [P, P, I64, U64, P],
     "haste_sgd_sr_update": [P, P, P, I64, I64, I64, F32, F32, F32, U64, U32, U32, P],
     "haste_dxt_to_dx_sr": [P, P, I64, I64, U64, P],

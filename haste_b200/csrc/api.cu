@@ -5,6 +5,7 @@
 #include "launchers.h"
 
 #include <string.h>
+#include <stdlib.h>
 
 namespace haste {
 
@@ -35,6 +36,19 @@ int validate_shape(const char* who, int64_t B, int64_t D, int64_t F, int64_t L, 
   if (B >= (1ll << 24)) return fail(HASTE_ERR_UNSUPPORTED, "%s: batch %lld too large (< 2^24)", who, (long long)B);
   if (D >= (1ll << 31) || (L + G - 1) / G >= (1ll << 31)) return fail(HASTE_ERR_UNSUPPORTED, "%s: D or group count exceeds int32", who);
   return HASTE_OK;
+}
+
+// Shape dispatch of the fused step: the tcgen05 kernel where its tile shapes apply (G=128, F=64, B%8==0,
+// no momentum), the warp-mma kernel for every other supported shape.  HASTE_STEP_IMPL=mma in the environment
+// forces the latter (used to compare the two kernels on the same inputs).
+int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
+                      const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
+                      cudaStream_t st, const StepDump* dump) {
+  static const bool force_mma = [] { const char* e = getenv("HASTE_STEP_IMPL"); return e != nullptr && strcmp(e, "mma") == 0; }();
+  if (!force_mma && train_step_sm100_supported(B, F, G, u))
+    return launch_train_step_sm100(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st, dump);
+  if (dump != nullptr) return fail(HASTE_ERR_UNSUPPORTED, "debug outputs exist only in the tcgen05 fused step (G=128, F=64, B%%8==0, no momentum)");
+  return launch_train_step_mma(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);
 }
 
 }  // namespace haste
@@ -111,11 +125,11 @@ int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_
   return launch_targets_bucket(coo, nnz, label0, L, G, tgt_ptr, tgt_ent, scratch, static_cast<cudaStream_t>(stream));
 }
 
-int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
+static int train_step_impl(const StepDump* dump, const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
                          const uint32_t* tgt_ent, float* dxt, float* loss, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G,
                          int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step,
                          uint32_t flags, haste_stream_t stream) {
-  const char* who = "haste_ffi_train_step";
+  const char* who = dump ? "haste_ffi_train_step_dbg" : "haste_ffi_train_step";
   REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(tgt_ptr, who); REQUIRE_PTR(dxt, who);
   REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(dxt, who);
   if (mom_w) REQUIRE_ALIGNED(mom_w, who);
@@ -131,7 +145,25 @@ int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias
   u.w = static_cast<__nv_bfloat16*>(w); u.bias = static_cast<__nv_bfloat16*>(bias);
   u.mom_w = (mu != 0.f) ? mom_w : nullptr; u.mom_b = (mu != 0.f) ? mom_b : nullptr;
   u.lr = lr; u.wd = wd; u.mu = mu; u.seed = seed; u.step = step; u.flags = flags; u.label0 = label0;
-  return launch_train_step(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);
+  return launch_train_step(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st, dump);
+}
+
+int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
+                         const uint32_t* tgt_ent, float* dxt, float* loss, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G,
+                         int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step,
+                         uint32_t flags, haste_stream_t stream) {
+  return train_step_impl(nullptr, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, B, D, F, L, G, label0, loss_kind, grad_scale,
+                         lr, wd, mu, seed, step, flags, stream);
+}
+
+int haste_ffi_train_step_dbg(const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
+                             const uint32_t* tgt_ent, float* dxt, float* loss, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G,
+                             int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed,
+                             uint32_t step, uint32_t flags, void* z_dump, int64_t ldz, void* dw_dump, void* dbias_dump,
+                             haste_stream_t stream) {
+  StepDump d{z_dump, ldz, dw_dump, dbias_dump};
+  return train_step_impl(&d, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, B, D, F, L, G, label0, loss_kind, grad_scale, lr,
+                         wd, mu, seed, step, flags, stream);
 }
 
 int haste_sr_round(const float* x, void* out, int64_t n, uint64_t seed, haste_stream_t stream) {

@@ -585,11 +585,3 @@ int launch_train_step_mma(const int32_t* loc, const void* xt, const int32_t* tgt
 
 }  // namespace haste
 
-namespace haste {
-// The fused step currently has one implementation for every shape.
-int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
-                      const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
-                      cudaStream_t st) {
-  return launch_train_step_mma(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);
-}
-}  // namespace haste

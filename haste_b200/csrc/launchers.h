@@ -27,9 +27,21 @@ int launch_bwd_weights(const void* xt, const int32_t* loc, const void* dy, void*
 int launch_train_step_mma(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
                           const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
                           cudaStream_t st);
+// Optional debug outputs of the tcgen05 fused step (tests only).
+struct StepDump {
+  void* z;       // bf16 [B, ldz] logits as rounded by the epilogue
+  int64_t ldz;
+  void* dw;      // bf16 [L,F] weight gradient consumed by the update
+  void* dbias;   // bf16 [L]
+};
+
+bool train_step_sm100_supported(int64_t B, int64_t F, int64_t G, const UpdateArgs& u);
+int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
+                            const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
+                            cudaStream_t st, const StepDump* dump = nullptr);
 int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
                       const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
-                      cudaStream_t st);
+                      cudaStream_t st, const StepDump* dump = nullptr);
 int launch_sr_round(const float* x, void* out, int64_t n, uint64_t seed, cudaStream_t st);
 int launch_sgd_sr(void* w, const void* g, float* m, int64_t rows, int64_t cols, int64_t row0, float lr, float wd, float mu, uint64_t seed,
                   uint32_t step, uint32_t flags, cudaStream_t st);

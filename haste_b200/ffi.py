@@ -127,6 +127,22 @@ def train_step(loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, l
                                        mu, seed, step, flags, _stream(xt)), "ffi_train_step")
 
 
+def train_step_dbg(loc, xt, w, bias, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, seed, step, flags):
+    """The fused step with debug outputs: returns (z bf16 [B,L], dw bf16 [L,F], dbias bf16 [L])."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    z = torch.zeros(B, L, dtype=torch.bfloat16, device=xt.device)
+    dw = torch.zeros(L, F, dtype=torch.bfloat16, device=xt.device)
+    db = torch.zeros(L, dtype=torch.bfloat16, device=xt.device)
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_train_step_dbg(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), None, None, _ptr(tgt_ptr), _ptr(tgt_ent),
+                                           _ptr(dxt), _ptr(loss), B, D, F, L, G, label0, loss_kind, grad_scale, lr, wd, 0.0, seed,
+                                           step, flags, _ptr(z), L, _ptr(dw), _ptr(db) if bias is not None else None, _stream(xt)),
+              "ffi_train_step_dbg")
+    return z, dw, db
+
+
 def sr_round(x, out, seed):
     _req(x, "x", torch.float32); _req(out, "output", torch.bfloat16)
     with torch.cuda.device(x.device):

@@ -113,6 +113,19 @@ int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias
                          int32_t loss_kind, float grad_scale, float lr, float wd, float mu,
                          uint64_t seed, uint32_t step, uint32_t flags, haste_stream_t stream);
 
+/* Same step with debug outputs (tests): z_dump bf16 [B,ldz] receives the logits as the epilogue rounded them,
+ * dw_dump bf16 [L,F] / dbias_dump bf16 [L] the gradients the update consumed; any of them may be NULL.
+ * Only the tcgen05 kernel (G=128, F=64, B%8==0, no momentum) implements them; other shapes return
+ * HASTE_ERR_UNSUPPORTED.  No counterpart in the reference (its logits and gradients are ordinary tensors). */
+int haste_ffi_train_step_dbg(const int32_t* loc, const void* xt, void* w, void* bias,
+                             float* mom_w, float* mom_b,
+                             const int32_t* tgt_ptr, const uint32_t* tgt_ent,
+                             float* dxt, float* loss,
+                             int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t label0,
+                             int32_t loss_kind, float grad_scale, float lr, float wd, float mu,
+                             uint64_t seed, uint32_t step, uint32_t flags,
+                             void* z_dump, int64_t ldz, void* dw_dump, void* dbias_dump, haste_stream_t stream);
+
 /* Elementwise stochastic rounding fp32 -> bf16 with the reference stream over the flat index.
  * Replaces sr_triton.stochastic_rounding (shared_ffi/sr_triton.py:27-59). */
 int haste_sr_round(const float* x, void* out, int64_t n, uint64_t seed, haste_stream_t stream);

@@ -371,7 +371,7 @@ def make_inputs(B, D, L, F, G, avg_pos, zipf_s, seed=42, x_kind='l2norm', bias_z
     NG = (L + G - 1) // G
     rs = np.random.RandomState(seed)
     keys = rs.rand(NG, D).astype(np.float32)
-    loc = np.sort(np.argpartition(keys, F, axis=1)[:, :F], axis=1).astype(np.int32)
+    loc = np.sort(np.argsort(keys, axis=1, kind='stable')[:, :F], axis=1).astype(np.int32)
     bias = torch.zeros(L, dtype=torch.bfloat16)
     if not bias_zero:
         bias = (torch.randn(L, generator=gen) * 0.1).to(torch.bfloat16)

@@ -1,0 +1,111 @@
+"""GPU parity tests of the tcgen05 fused train step (group size 128, fan-in 64) through the C ABI.
+
+The kernel's debug outputs expose the bf16 logits and the bf16 gradients it consumed, which splits the check
+into (a) tensor-core products against the oracle within the floating-point tolerance (rel 1e-2 / abs 1e-3 of
+the magnitude) and (b) everything downstream of them — loss gradient (squared hinge is exact arithmetic),
+SGD + weight decay + stochastic rounding — bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import ffi_oracle as fo
+
+F, G = 64, 128
+SHAPES = [(200, 256, 1111), (512, 768, 5000), (128, 128, 384), (1024, 300, 2000), (8, 96, 100), (392, 768, 20000)]  # B, D, L
+
+
+@pytest.fixture(scope="module")
+def hb():
+    import haste_b200.ffi as ffi
+    import haste_b200._lib as lib
+    return ffi, lib
+
+
+def _bits(t):
+    return fo._bf16_to_bits(t.detach().cpu())
+
+
+def _close(got, want, rel, abs_, what):
+    got, want = got.float().cpu(), want.float().cpu()
+    bad = (got - want).abs() > abs_ + rel * want.abs()
+    assert not bad.any(), f"{what}: {int(bad.sum())}/{bad.numel()} outside tolerance, max err {float((got - want).abs().max())}"
+
+
+def _run(ffi, lib, inp, B, D, L, kind, scale, rng, label0=0, bias=True, step=3, seed=123, lr=0.05, wd=1e-4):
+    dev = {k: v.cuda() for k, v in inp.items()}
+    xt = dev["X"].t().contiguous()
+    NG = (L + G - 1) // G
+    coo = dev["targets"].clone()
+    coo[:, 1] += label0
+    ptr = torch.zeros(NG + 1, dtype=torch.int32, device="cuda")
+    ent = torch.zeros(max(1, coo.shape[0]), dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(NG, dtype=torch.int32, device="cuda")
+    ffi.targets_bucket(coo, label0, L, G, ptr, ent, scratch)
+    w = dev["W"].clone()
+    b = dev["bias"].clone() if bias else None
+    dxt = torch.full((D, B), 3.0, dtype=torch.float32, device="cuda")
+    loss = torch.zeros(1, dtype=torch.float32, device="cuda")
+    flags = ffi.make_flags(sr=True, contract=True, rng=rng, zero_dxt=True, loss=True)
+    z, dw, db = ffi.train_step_dbg(dev["loc"], xt, w, b, ptr, ent, dxt, loss, G, label0, kind, scale, lr, wd, seed, step, flags)
+    torch.cuda.synchronize()
+    return w, b, dxt, float(loss), z, dw, db
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("rng", ["packed", "reference"])
+def test_sm100_step_hinge_chain(hb, shape, rng):
+    ffi, lib = hb
+    B, D, L = shape
+    inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=B + L, x_kind="normal", bias_zero=False)
+    scale, label0 = 0.5, 384
+    w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, scale, rng, label0=label0)
+    # (a) tensor-core products within tolerance
+    z_ref = fo.forward(inp["loc"], inp["X"], inp["W"], inp["bias"], G, round_bf16=False)
+    _close(z, z_ref, 1e-2, 1e-3 * max(1.0, float(z_ref.abs().max())), "logits")
+    loss_ref, dY = fo.loss_and_grad(z.cpu(), inp["targets"], fo.LOSS_SQHINGE, scale)       # exact given the kernel's logits
+    dw_ref = fo.backward_weights(inp["loc"], inp["X"], dY, G, L, round_bf16=False)
+    _close(dw, dw_ref, 1e-2, 1e-3 * max(1.0, float(dw_ref.abs().max())), "dW")
+    _close(db, dY.float().sum(0), 1e-2, 1e-3 * max(1.0, float(dY.float().sum(0).abs().max())), "dbias")
+    dxt_ref = fo.backward_features(inp["loc"], inp["W"], dY, G, D)
+    _close(dxt, dxt_ref, 1e-2, 1e-3 * max(1.0, float(dxt_ref.abs().max())), "dXt")
+    assert abs(loss - loss_ref) <= 1e-3 * abs(loss_ref) + 1e-3
+    # (b) the update, bit for bit, from the gradients the kernel consumed
+    want_w, _ = fo.sgd_update(inp["W"], dw.cpu(), None, 0.05, 1e-4, 0.0, False, True, fo.rand16_for((L, F), 123, 3, rng, label0))
+    want_b, _ = fo.sgd_update(inp["bias"], db.cpu(), None, 0.05, 1e-4, 0.0, False, True,
+                              fo.rand16_for((L, 1), 123, 3, rng, label0, is_bias=True).reshape(L))
+    assert np.array_equal(_bits(w), fo._bf16_to_bits(want_w)), "weights"
+    assert np.array_equal(_bits(b), fo._bf16_to_bits(want_b)), "bias"
+
+
+@pytest.mark.parametrize("shape", [(200, 256, 1111), (512, 768, 5000), (8, 96, 100)])
+def test_sm100_step_bce_and_nobias(hb, shape):
+    ffi, lib = hb
+    B, D, L = shape
+    inp = fo.make_inputs(B, D, L, F, G, 12, 1.1, seed=7, x_kind="normal", bias_zero=False)
+    for bias in (True, False):
+        w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_BCE, 1.0, "packed", bias=bias)
+        bias_t = inp["bias"] if bias else None
+        z_ref = fo.forward(inp["loc"], inp["X"], inp["W"], bias_t, G, round_bf16=False)
+        _close(z, z_ref, 1e-2, 1e-3 * max(1.0, float(z_ref.abs().max())), "logits")
+        loss_ref, dY = fo.loss_and_grad(z.cpu(), inp["targets"], fo.LOSS_BCE, 1.0)
+        assert abs(loss - loss_ref) <= 2e-3 * abs(loss_ref)
+        dw_ref = fo.backward_weights(inp["loc"], inp["X"], dY, G, L, round_bf16=False)
+        _close(dw, dw_ref, 2e-2, 2e-3 * max(1.0, float(dw_ref.abs().max())), "dW")      # sigmoid via fast exp: dY may differ by a bf16 step
+        dxt_ref = fo.backward_features(inp["loc"], inp["W"], dY, G, D)
+        _close(dxt, dxt_ref, 2e-2, 2e-3 * max(1.0, float(dxt_ref.abs().max())), "dXt")
+        want_w, _ = fo.sgd_update(inp["W"], dw.cpu(), None, 0.05, 1e-4, 0.0, False, True, fo.rand16_for((L, F), 123, 3, "packed", 0))
+        assert np.array_equal(_bits(w), fo._bf16_to_bits(want_w))
+
+
+def test_sm100_step_repeatable_weights(hb):
+    """Two runs on the same inputs give identical weights (the tensor-core products and the update are
+    deterministic; only the dX atomics may reorder)."""
+    ffi, lib = hb
+    B, D, L = 512, 768, 9000
+    inp = fo.make_inputs(B, D, L, F, G, 6, 1.0, seed=5, bias_zero=False)
+    r1 = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, 1.0, "packed")
+    r2 = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, 1.0, "packed")
+    assert torch.equal(r1[0], r2[0]) and torch.equal(r1[1], r2[1])
+    assert torch.allclose(r1[2], r2[2], rtol=1e-5, atol=1e-5 * float(r1[2].abs().max()))
