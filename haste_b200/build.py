@@ -47,6 +47,10 @@ def _compile(src, force):
 
 
 def build(force=False, verbose=False):
+    extra = os.environ.get("HASTE_EXTRA_NVCC", "").split()      # development builds (e.g. -DHASTE_TRACE); forces a rebuild
+    if extra:
+        NVCC_FLAGS.extend(f for f in extra if f not in NVCC_FLAGS)
+        force = True
     os.makedirs(OBJ, exist_ok=True)
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         results = list(ex.map(lambda s: _compile(s, force), SOURCES))

@@ -10,16 +10,18 @@
 //   backward-features  dXg[b,k] (TMEM,  64 cols)  = Y (K-major A)   * W (MN-major B),        K = G
 //   backward-weights   dW [l,k] (TMEM, 64+16 cols, accumulated over the batch tiles)
 //                                                 = Y^T(MN-major A) * X (K-major B),          K = 128
-// Warp roles (512 threads): warp 0 producer (cp.async gather of X tiles through a 4-stage ring, W double
-// buffered), warp 1 issues every tcgen05.mma, warps 4-11 turn Z into dY (bias, bf16 rounding, loss gradient,
-// target bits) and store it swizzled, warps 12-15 drain dXg (TMEM -> fp32 staging -> bulk reduce-add into
-// dxt rows) and at the end of a group apply SGD + weight decay + stochastic rounding to the weights and bias
-// straight from the dW accumulator.  Logits, dY and dW never reach global memory.
+// Warp roles (512 threads): warps 0,2,3 producers (cp.async gather of X tiles through a 6-stage ring, W double
+// buffered; load items are dealt round-robin so three are in flight), warp 1 issues every tcgen05.mma,
+// warps 4-11 turn Z into dY (bias, bf16 rounding, loss gradient, target bits) and store it swizzled,
+// warps 12-15 drain dXg (TMEM -> registers -> coalesced red.global.add into dxt rows) and at the end of a
+// group apply SGD + weight decay + stochastic rounding to the weights and bias straight from the dW
+// accumulator.  Logits, dY and dW never reach global memory.
 // All hand-offs are mbarriers with bounded waits; a wait that gives up raises a CTA-wide abort flag, every
 // role drains its loops without touching global memory, TMEM is freed and the host sees HASTE_ERR_TIMEOUT.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100.cuh"
+#include <stdlib.h>
 
 namespace haste {
 namespace s100 {
@@ -27,18 +29,16 @@ using namespace sm100;
 
 constexpr int G = 128, F = 64, BT = 128;
 constexpr int FR = F + 16;                    // rows of an X block: F gathered rows, one row of ones, 15 zero rows
-constexpr int NXS = 4;                        // X ring stages
+constexpr int NXS = 6;                        // X ring stages
 constexpr int XBLK = FR * 128;                // one 64-batch block of an X stage (bytes)
 constexpr int XSTAGE = 2 * XBLK;
 constexpr int WSTAGE = G * 128;
 constexpr int YBLK = BT * 128;
 constexpr int YSTAGE = 2 * YBLK;
-constexpr int STG = F * BT * 4;
 constexpr int OFF_X = 0;
 constexpr int OFF_W = OFF_X + NXS * XSTAGE;
 constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
-constexpr int OFF_STG = OFF_Y + 2 * YSTAGE;
-constexpr int OFF_BIAS = OFF_STG + STG;              // float [2][G]
+constexpr int OFF_BIAS = OFF_Y + 2 * YSTAGE;         // float [2][G]
 constexpr int OFF_LOC = OFF_BIAS + 2 * G * 4;        // int   [2][F]
 constexpr int OFF_YB = OFF_LOC + 2 * F * 4;          // u32   [2][BT][4]  target bits
 constexpr int OFF_BAR = OFF_YB + 2 * BT * 4 * 4;     // mbarriers
@@ -57,6 +57,18 @@ static_assert(NBAR <= 32, "barrier space");
 constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
 constexpr int NTHREADS = 512;
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
+
+#ifdef HASTE_TRACE
+// development build only: per-role event timeline of CTA 0
+__device__ long long g_trace[4][2048][2];
+__device__ int g_trace_n[4];
+#define TR(role, ev)                                                        \
+  do {                                                                      \
+    if (blockIdx.x == 0 && tr_n < 2048) { g_trace[role][tr_n][0] = (ev); g_trace[role][tr_n][1] = clock64(); ++tr_n; g_trace_n[role] = tr_n; } \
+  } while (0)
+#else
+#define TR(role, ev) do {} while (0)
+#endif
 
 struct StepArgs {
   const int32_t* loc;
@@ -119,7 +131,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     *reinterpret_cast<uint4*>(sm + OFF_X + blk * XBLK + (F + row) * 128 + chunk * 16) = make_uint4(v, v, v, v);
   }
   fence_proxy_async();
-  if (warp == 2) {
+  if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TM_COLS);
     tmem_relinquish();
   }
@@ -128,49 +140,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  int tr_n = 0;   // trace cursor of this thread (development builds)
+  (void)tr_n;
   const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
 
-  if (warp == 0) {
-    // ================================================================ producer
-    uint32_t pend[2] = {0u, 0u};   // full-barriers of the two most recent items, not yet signalled
-    int npend = 0;
-    auto flush_all = [&]() {
+  if (warp == 0 || warp == 2 || warp == 3) {
+    // ================================================================ producers
+    // The sequence of load items (per group: the W item, then one X item per batch tile) is dealt round-robin to
+    // the three producer warps; each handles one item at a time: wait for the slot, issue the copies, wait for
+    // them to land, make them visible to the tensor core's proxy, signal "full".
+    const int p = (warp == 0) ? 0 : warp - 1;
+    int item = 0, it = 0;
+    auto land = [&](uint32_t full_bar) {
+      cp_async_commit();
       cp_async_wait<0>();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { if (npend > 0) mbar_arrive(pend[0]); if (npend > 1) mbar_arrive(pend[1]); }
-      npend = 0;
+      if (lane == 0) mbar_arrive(full_bar);
     };
-    auto wait_empty = [&](uint32_t b, uint32_t parity) {
-      // never sleep on an empty-slot barrier while earlier items still await their "full" signal
-      const bool ready = __all_sync(0xffffffffu, mbar_try_wait(b, parity));     // warp-uniform decision
-      if (!ready) { if (npend) flush_all(); mbar_wait(b, parity, abort_flag, a.err, 1, WAIT_LIMIT); __syncwarp(); }
-    };
-    auto item_done = [&](uint32_t full_bar) {
-      cp_async_commit();
-      if (npend == 2) {           // the oldest pending item has landed once at most 2 groups are in flight
-        cp_async_wait<2>();
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(pend[0]);
-        pend[0] = pend[1];
-        npend = 1;
-      }
-      pend[npend++] = full_bar;
-    };
-    int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
       const int64_t l0 = static_cast<int64_t>(g) * G;
       const int rows_real = static_cast<int>(imin64(G, a.L - l0));
-      // ---- W item: weights tile, index row, bias row
-      wait_empty(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1);
-      wait_empty(bar(B_MEMPTY + ws), ((gi >> 1) & 1) ^ 1);
-      {
-        const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
-        loc_s[ws * F + lane] = min(max(__ldg(lrow + lane), 0), a.D - 1);
-        loc_s[ws * F + lane + 32] = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
+      const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
+      const int loc_lo = min(max(__ldg(lrow + lane), 0), a.D - 1);        // clamped: never addresses outside xt / dxt
+      const int loc_hi = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
+      if (item % 3 == p) {
+        // ---- W item: weights tile, index row, bias row
+        mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
+        mbar_wait(bar(B_MEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
+        __syncwarp();
+        loc_s[ws * F + lane] = loc_lo;
+        loc_s[ws * F + lane + 32] = loc_hi;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int c = lane * 4 + i;
@@ -182,53 +184,70 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           const int idx = i * 32 + lane, r = idx >> 3, c = idx & 7;
           cp_async16(wb + r * 128 + ((c ^ (r & 7)) << 4), u.w + (l0 + r) * F + c * 8, r < rows_real);
         }
-        __syncwarp();
+        if (lane == 0) TR(0, 100 + gi);
+        land(bar(B_WFULL + ws));
       }
-      item_done(bar(B_WFULL + ws));
+      ++item;
       // ---- X items: one per batch tile
-      for (int t = 0; t < T; ++t, ++it) {
+      for (int t = 0; t < T; ++t, ++it, ++item) {
+        if (item % 3 != p) continue;
         const int xs = it % NXS;
-        wait_empty(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1);
+        mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
+        __syncwarp();
         const int64_t b0 = static_cast<int64_t>(t) * BT;
         const uint32_t xb = sbase + OFF_X + xs * XSTAGE;
         const int j = lane & 15;                     // 16-byte chunk along the batch: 8 rows each
         const bool valid = b0 + j * 8 < a.B;
-        const uint32_t dcol = (j >> 3) * XBLK;
+        const uint32_t dcol = (j >> 3) * XBLK + ((j & 7) << 4);
 #pragma unroll 4
         for (int i = 0; i < 32; ++i) {
           const int k = i * 2 + (lane >> 4);
-          const __nv_bfloat16* src = a.xt + static_cast<int64_t>(loc_s[ws * F + k]) * a.B + b0 + j * 8;
-          cp_async16(xb + dcol + k * 128 + (((j & 7) ^ (k & 7)) << 4), valid ? src : a.xt, valid);
+          const int lk = __shfl_sync(0xffffffffu, (i < 16) ? loc_lo : loc_hi, k & 31);
+          const __nv_bfloat16* src = a.xt + static_cast<int64_t>(lk) * a.B + b0 + j * 8;
+          cp_async16(xb + ((dcol + k * 128) ^ ((k & 7) << 4)), valid ? src : a.xt, valid);
         }
-        item_done(bar(B_XFULL + xs));
+        if (lane == 0) TR(0, 1000 + it);
+        land(bar(B_XFULL + xs));
       }
     }
-    flush_all();
   } else if (warp == 1) {
     // ================================================================ MMA issuer (one thread)
     if (lane == 0) {
       constexpr uint32_t ID_FWD = make_idesc(128, G, 1, 0);
       constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
       constexpr uint32_t ID_BWW = make_idesc(128, N_DW, 1, 0);
+      // Descriptors are built once; per MMA only the start-address field moves (the offsets below are in
+      // 16-byte units and never carry out of that 14-bit field because every operand lies inside the CTA's
+      // shared memory window).
+      const uint64_t D_XA = make_sdesc(sbase + OFF_X, XBLK, 1024);    // X tile as MN-major A   (forward)
+      const uint64_t D_XB = make_sdesc(sbase + OFF_X, 16, 1024);      // X tile as K-major  B   (backward-weights)
+      const uint64_t D_WB = make_sdesc(sbase + OFF_W, 16, 1024);      // W tile as K-major  B   (forward)
+      const uint64_t D_WM = make_sdesc(sbase + OFF_W, WSTAGE, 1024);  // W tile as MN-major B   (backward-features)
+      const uint64_t D_YA = make_sdesc(sbase + OFF_Y, 16, 1024);      // Y tile as K-major  A   (backward-features)
+      const uint64_t D_YM = make_sdesc(sbase + OFF_Y, YBLK, 1024);    // Y tile as MN-major A   (backward-weights)
       int it = 0;
       auto backward = [&](int j, int t, int ws, int gi) {
-        const int ys = j & 1;
+        const int ys = j & 1, xs = j % NXS;
         mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 2, WAIT_LIMIT);
         mbar_wait(bar(B_DXEMPTY + ys), ((j >> 1) & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
         if (t == 0) mbar_wait(bar(B_DWEMPTY), (gi & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
         tc_fence_after();
-        const uint32_t yb = sbase + OFF_Y + ys * YSTAGE, wb = sbase + OFF_W + ws * WSTAGE, xb = sbase + OFF_X + (j % NXS) * XSTAGE;
+        TR(1, 2000 + j);
+        const uint64_t dya = D_YA + static_cast<uint64_t>(ys * (YSTAGE >> 4)), dym = D_YM + static_cast<uint64_t>(ys * (YSTAGE >> 4));
+        const uint64_t dwm = D_WM + static_cast<uint64_t>(ws * (WSTAGE >> 4)), dxb = D_XB + static_cast<uint64_t>(xs * (XSTAGE >> 4));
+        const uint32_t tdx = tmem + TM_DX + ys * F;
 #pragma unroll
         for (int ks = 0; ks < G / 16; ++ks)      // dXg[b,k] += Y[b, l-chunk] * W[l-chunk, k]
-          umma_bf16(tmem + TM_DX + ys * F, make_sdesc(yb + (ks >> 2) * YBLK + (ks & 3) * 32, 16, 1024),
-                    make_sdesc(wb + ks * 2048, WSTAGE, 1024), ID_BWX, ks > 0);
+          umma_bf16(tdx, dya + static_cast<uint64_t>(((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), dwm + static_cast<uint64_t>((ks * 2048) >> 4),
+                    ID_BWX, ks > 0);
         tc_commit(bar(B_DXFULL + ys));
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks)     // dW[l,k] += Y[b-chunk, l]^T * X[k, b-chunk]
-          umma_bf16(tmem + TM_DW, make_sdesc(yb + ks * 2048, YBLK, 1024),
-                    make_sdesc(xb + (ks >> 2) * XBLK + (ks & 3) * 32, 16, 1024), ID_BWW, (t > 0) || (ks > 0));
+          umma_bf16(tmem + TM_DW, dym + static_cast<uint64_t>((ks * 2048) >> 4),
+                    dxb + static_cast<uint64_t>(((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), ID_BWW, (t > 0) || (ks > 0));
         tc_commit(bar(B_YEMPTY + ys));
-        tc_commit(bar(B_XEMPTY + (j % NXS)));
+        tc_commit(bar(B_XEMPTY + xs));
+        TR(1, 3000 + j);
       };
       for (int gi = 0; gi < n_my_groups; ++gi) {
         const int ws = gi & 1;
@@ -238,10 +257,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           mbar_wait(bar(B_XFULL + xs), (it / NXS) & 1, abort_flag, a.err, 6, WAIT_LIMIT);
           mbar_wait(bar(B_ZEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 7, WAIT_LIMIT);
           tc_fence_after();
-          const uint32_t xb = sbase + OFF_X + xs * XSTAGE, wb = sbase + OFF_W + ws * WSTAGE;
+          TR(1, 1000 + it);
+          const uint64_t dxa = D_XA + static_cast<uint64_t>(xs * (XSTAGE >> 4)), dwb = D_WB + static_cast<uint64_t>(ws * (WSTAGE >> 4));
+          const uint32_t tz = tmem + TM_Z + zs * G;
 #pragma unroll
           for (int ks = 0; ks < F / 16; ++ks)    // Z[b,l] += X[k-chunk, b]^T * W[l, k-chunk]
-            umma_bf16(tmem + TM_Z + zs * G, make_sdesc(xb + ks * 2048, XBLK, 1024), make_sdesc(wb + ks * 32, 16, 1024), ID_FWD, ks > 0);
+            umma_bf16(tz, dxa + static_cast<uint64_t>((ks * 2048) >> 4), dwb + static_cast<uint64_t>((ks * 32) >> 4), ID_FWD, ks > 0);
           tc_commit(bar(B_ZFULL + zs));
           if (t > 0) backward(it - 1, t - 1, ws, gi);
         }
@@ -284,55 +305,94 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         const bool row_valid = b0 + row < a.B;
         const float gs = row_valid ? a.grad_scale : 0.f;
         mbar_wait(bar(B_ZFULL + zs), (it >> 1) & 1, abort_flag, a.err, 9, WAIT_LIMIT);
+        if (ea == 0 && lane == 0) TR(2, 1000 + it);
         mbar_wait(bar(B_YEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
         tc_fence_after();
+        if (ea == 0 && lane == 0) TR(2, 2000 + it);
         uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + h * YBLK + row * 128;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + h * 64;
+        const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + h * 64);
+        const float gs2 = 2.f * gs;
+        const bool ragged = h * 64 + 64 > rows_real;   // only the last group of the layer can be ragged
+        const uint64_t ym64 = static_cast<uint64_t>(ym[0]) | (static_cast<uint64_t>(ym[1]) << 32);
+        float tile_loss = 0.f;
+        // 16-column chunks, software-pipelined (the TMEM load of the next chunk is in flight while this one is
+        // processed) in a real loop: four roles share each scheduler's instruction cache, so code stays small.
+        auto process16 = [&](const uint32_t (&r)[16], int c16) {
+          const uint32_t ym16 = static_cast<uint32_t>(ym64 >> c16) & 0xFFFFu;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + h * 64 + c * 32, r);
-          tmem_ld_wait();
-          if (c == 1) {                              // this warp's part of the Z stage is now in registers
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
-          }
-          const int colbase = h * 64 + c * 32;
-          const float* bs = bias_s + ws * G + colbase;
-          const uint32_t ymask = ym[c];
-          const bool ragged = colbase + 32 > rows_real;
-#pragma unroll
-          for (int e8 = 0; e8 < 32; e8 += 8) {
-            uint32_t pk[4];
+          for (int e8 = 0; e8 < 16; e8 += 8) {
+            float z[8];
+            {
+              const float4 ba = bs4[(c16 + e8) >> 2], bb = bs4[((c16 + e8) >> 2) + 1];
+              z[0] = __uint_as_float(r[e8 + 0]) + ba.x; z[1] = __uint_as_float(r[e8 + 1]) + ba.y;
+              z[2] = __uint_as_float(r[e8 + 2]) + ba.z; z[3] = __uint_as_float(r[e8 + 3]) + ba.w;
+              z[4] = __uint_as_float(r[e8 + 4]) + bb.x; z[5] = __uint_as_float(r[e8 + 5]) + bb.y;
+              z[6] = __uint_as_float(r[e8 + 6]) + bb.z; z[7] = __uint_as_float(r[e8 + 7]) + bb.w;
+            }
+            uint32_t zp[4];                            // logits rounded to bf16, as the unfused forward stores them
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-              float gq[2];
+              zp[p] = pack_bf16x2(z[2 * p], z[2 * p + 1]);
+              z[2 * p] = __uint_as_float(zp[p] << 16);
+              z[2 * p + 1] = __uint_as_float(zp[p] & 0xFFFF0000u);
+            }
+            const uint32_t ym8 = (ym16 >> e8) & 0xFFu;
+            float gq[8];
+            if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
+              // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
 #pragma unroll
-              for (int x = 0; x < 2; ++x) {
-                const int e = e8 + 2 * p + x;
-                const float zv = round_to_bf16_f(__uint_as_float(r[e]) + bs[e]);
-                float la = 0.f;
-                float gl = loss_grad<LOSS, WITH_LOSS>(zv, (ymask >> e) & 1u, la);
-                if (ragged && colbase + e >= rows_real) { gl = 0.f; la = 0.f; }
-                if (WITH_LOSS) loss_acc += row_valid ? la : 0.f;
-                gq[x] = gl * gs;
+              for (int i = 0; i < 8; ++i) {
+                const float ns = __uint_as_float(0x3F800000u | (((ym8 >> i) & 1u) << 31));
+                const float m = fmaxf(fmaf(ns, z[i], 1.f), 0.f);
+                gq[i] = (ns * m) * gs2;
+                if (WITH_LOSS) tile_loss = fmaf(m, m, tile_loss);
               }
-              pk[p] = pack_bf16x2(gq[0], gq[1]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float la = 0.f;
+                float gl = loss_grad<LOSS, WITH_LOSS>(z[i], (ym8 >> i) & 1u, la);
+                if (ragged && h * 64 + c16 + e8 + i >= rows_real) { gl = 0.f; la = 0.f; }
+                if (WITH_LOSS) tile_loss += la;
+                gq[i] = gl * gs;
+              }
             }
             if (a.z_dump != nullptr && row_valid) {
+              uint16_t* zd = reinterpret_cast<uint16_t*>(a.z_dump) + (b0 + row) * a.ldz + static_cast<int64_t>(g) * G + h * 64 + c16 + e8;
 #pragma unroll
-              for (int e = e8; e < e8 + 8; ++e)
-                if (colbase + e < rows_real)
-                  a.z_dump[(b0 + row) * a.ldz + static_cast<int64_t>(g) * G + colbase + e] =
-                      __float2bfloat16_rn(__uint_as_float(r[e]) + bs[e]);
+              for (int i = 0; i < 8; ++i)
+                if (h * 64 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>((i & 1) ? (zp[i >> 1] >> 16) : (zp[i >> 1] & 0xFFFFu));
             }
-            const int chunk = (c * 32 + e8) >> 3;    // 16-byte chunk inside the 128-byte row of this block
-            *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(ytile + ((((c16 + e8) >> 3) ^ (row & 7)) << 4)) =
+                make_uint4(pack_bf16x2(gq[0], gq[1]), pack_bf16x2(gq[2], gq[3]), pack_bf16x2(gq[4], gq[5]), pack_bf16x2(gq[6], gq[7]));
+          }
+        };
+        {
+          uint32_t ra[16], rb[16];
+          tmem_ld16(ta, ra);
+          tmem_ld_wait();
+#pragma unroll 1
+          for (int c = 0; c < 64; c += 32) {
+            __syncwarp();
+            tmem_ld16(ta + c + 16, rb);
+            process16(ra, c);
+            tmem_ld_wait();
+            __syncwarp();
+            if (c + 32 < 64) tmem_ld16(ta + c + 32, ra);
+            process16(rb, c + 16);
+            tmem_ld_wait();
           }
         }
+        tc_fence_before();                             // this warp's half of the Z stage has been read
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
+        if (WITH_LOSS) loss_acc += row_valid ? tile_loss : 0.f;
+        if (ea == 0 && lane == 0) TR(2, 2700 + it);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_YFULL + zs));
+        if (ea == 0 && lane == 0) TR(2, 3000 + it);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));
@@ -347,7 +407,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     const int q = warp & 3;
     const int row = q * 32 + lane;               // TMEM lane: batch row (dXg) or label row (dW)
     const int bt = tid - 384;                    // 0..127
-    float* stg = reinterpret_cast<float*>(sm + OFF_STG);
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
@@ -355,87 +414,125 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       const int64_t l0 = static_cast<int64_t>(g) * G;
       const int rows_real = static_cast<int>(imin64(G, a.L - l0));
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 11, WAIT_LIMIT);
-      const int my_loc = loc_s[ws * F + (bt & (F - 1))];
+      const int4* loc4 = reinterpret_cast<const int4*>(loc_s + ws * F);
       for (int t = 0; t < T; ++t, ++it) {
         const int ds = it & 1;
         const int64_t b0 = static_cast<int64_t>(t) * BT;
         mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 12, WAIT_LIMIT);
         tc_fence_after();
-        uint32_t r0[32], r1[32];
+        if (bt == 0) TR(3, 1000 + it);
         const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + ds * F;
-        tmem_ld32(ta, r0);
-        tmem_ld32(ta + 32, r1);
-        tmem_ld_wait();
+        const bool live = (b0 + row < a.B) && !*abort_flag;
+        float* dbase = a.dxt + b0 + row;
+        // dXg[b,k] of this thread's batch row goes to dxt[loc[k], b]: for a fixed k the warp's 32 lanes hit 32
+        // consecutive floats, so each red below is one 128-byte transaction
+        auto scatter16 = [&](const uint32_t (&r)[16], int c16) {
+          if (!live) return;
+#pragma unroll
+          for (int k4 = 0; k4 < 16; k4 += 4) {
+            const int4 lc = loc4[(c16 + k4) >> 2];
+            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r[k4 + 0]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r[k4 + 1]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r[k4 + 2]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r[k4 + 3]));
+          }
+        };
+        {
+          uint32_t ra[16], rb[16];
+          tmem_ld16(ta, ra);
+          tmem_ld_wait();
+#pragma unroll 1
+          for (int c = 0; c < F; c += 32) {
+            __syncwarp();
+            tmem_ld16(ta + c + 16, rb);
+            scatter16(ra, c);
+            tmem_ld_wait();
+            __syncwarp();
+            if (c + 32 < F) tmem_ld16(ta + c + 32, ra);
+            scatter16(rb, c + 16);
+            tmem_ld_wait();
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_DXEMPTY + ds));
-        if (bt < F) bulk_wait_read<0>();           // the previous tile's reduce has finished reading the staging tile
-        named_bar_sync(2, 128);
-#pragma unroll
-        for (int k = 0; k < 32; ++k) { stg[k * BT + row] = __uint_as_float(r0[k]); stg[(k + 32) * BT + row] = __uint_as_float(r1[k]); }
-        fence_proxy_async();
-        named_bar_sync(2, 128);
-        if (bt < F && !*abort_flag) {
-          const uint32_t nvalid = static_cast<uint32_t>(imin64(BT, a.B - b0));
-          bulk_reduce_add_f32(a.dxt + static_cast<int64_t>(my_loc) * a.B + b0, smem_u32(stg + bt * BT), nvalid * 4u);
-          bulk_commit();
-        }
+        if (bt == 0) TR(3, 2000 + it);
       }
       // ---- weight / bias update from the dW accumulator
       mbar_wait(bar(B_DWFULL), gi & 1, abort_flag, a.err, 13, WAIT_LIMIT);
       tc_fence_after();
-      uint32_t r0[32], r1[32], rb[16];
+      if (bt == 0) TR(3, 5000 + gi);
       const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
-      tmem_ld32(ta, r0);
-      tmem_ld32(ta + 32, r1);
-      if (HAS_BIAS) tmem_ld16(ta + 64, rb);
-      tmem_ld_wait();
+      const bool do_upd = row < rows_real && !*abort_flag;
+      const int64_t l = l0 + row, gl = u.label0 + l;
+      const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
+      {
+        __nv_bfloat16* wrow = u.w + l * F;
+        const uint8_t* wsm = sm + OFF_W + ws * WSTAGE + row * 128;   // the group's W tile still holds the old weights
+#pragma unroll 1
+        for (int c8 = 0; c8 < F / 8; ++c8) {
+          uint32_t r[8];
+          __syncwarp();                                  // the loads below are warp-collective
+          tmem_ld8(ta + c8 * 8, r);
+          tmem_ld_wait();
+          if (!do_upd) continue;
+          uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
+          uint32_t* wp = reinterpret_cast<uint32_t*>(&wv);
+          uint32_t rnd[4] = {0u, 0u, 0u, 0u};          // 8 x 16 random bits, two per word
+          if (sr) {
+            if (packed) {
+              const uint4 rp = rand_packed8(u.seed, u.step, gl, c8);
+              rnd[0] = rp.x; rnd[1] = rp.y; rnd[2] = rp.z; rnd[3] = rp.w;
+            } else {
+#pragma unroll 1
+              for (int x = 0; x < 8; ++x) rnd[x >> 1] |= rand16_reference(u.seed, gl * F + c8 * 8 + x) << (16 * (x & 1));
+            }
+          }
+          uint32_t ob[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float a0 = __uint_as_float(r[2 * p]), a1 = __uint_as_float(r[2 * p + 1]);
+            if (a.dw_dump != nullptr) {
+              a.dw_dump[l * F + c8 * 8 + 2 * p] = __float2bfloat16_rn(a0);
+              a.dw_dump[l * F + c8 * 8 + 2 * p + 1] = __float2bfloat16_rn(a1);
+            }
+            // the gradient is first rounded to bf16, as the unfused kernel would store it
+            const uint32_t gp = pack_bf16x2(a0, a1);
+            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
+            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
+            float n0, n1;
+            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            const uint32_t b0 = sr ? ((__float_as_uint(n0) + (rnd[p] & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
+            const uint32_t b1 = sr ? ((__float_as_uint(n1) + (rnd[p] >> 16)) >> 16) : rn_bf16_bits(n1);
+            ob[p] = (b0 & 0xFFFFu) | (b1 << 16);
+          }
+          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+      }
+      uint32_t rb[8];
+      __syncwarp();
+      if (HAS_BIAS) { tmem_ld8(ta + F, rb); tmem_ld_wait(); }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
-      if (row < rows_real && !*abort_flag) {
-        const int64_t l = l0 + row, gl = u.label0 + l;
-        __nv_bfloat16* wrow = u.w + l * F;
-#pragma unroll
-        for (int c8 = 0; c8 < F / 8; ++c8) {
-          uint4 wv = *reinterpret_cast<const uint4*>(wrow + c8 * 8);
-          uint32_t* wp = reinterpret_cast<uint32_t*>(&wv);
-          uint4 rp = make_uint4(0, 0, 0, 0);
-          const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED;
-          if (sr && packed) rp = rand_packed8(u.seed, u.step, gl, c8);
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const int k = c8 * 8 + x;
-            const float acc = __uint_as_float(k < 32 ? r0[k & 31] : r1[k & 31]);
-            const float gr = round_to_bf16_f(acc);          // the gradient as the unfused kernel would store it
-            if (a.dw_dump != nullptr) a.dw_dump[l * F + k] = __float2bfloat16_rn(acc);
-            uint32_t r16 = 0;
-            if (sr) r16 = packed ? unpack16(rp, x) : rand16_reference(u.seed, gl * F + k);
-            const uint16_t wb = (wp[x >> 1] >> (16 * (x & 1))) & 0xFFFFu;
-            const uint16_t nb = sgd_update_bits(wb, gr, nullptr, u.lr, u.wd, u.mu, u.flags, r16);
-            wp[x >> 1] = (x & 1) ? ((wp[x >> 1] & 0xFFFFu) | (uint32_t(nb) << 16)) : ((wp[x >> 1] & 0xFFFF0000u) | nb);
-          }
-          *reinterpret_cast<uint4*>(wrow + c8 * 8) = wv;
-        }
-        if (HAS_BIAS) {
-          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
-          if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
-          uint32_t r16 = 0;
-          if (u.flags & HASTE_F_SR)
-            r16 = rand16(u.flags, u.seed ^ ((u.flags & HASTE_F_RNG_PACKED) ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
-          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
-        }
+      if (HAS_BIAS && do_upd) {
+        const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
+        if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
+        uint32_t r16 = 0;
+        if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
+        u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
       }
+      if (bt == 0) TR(3, 6000 + gi);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));
     }
-    if (bt < F) bulk_wait<0>();
   }
 
   // ---------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem, TM_COLS);
+  if (warp == 1) tmem_dealloc(tmem, TM_COLS);
 }
 
 static int* g_err_host = nullptr;   // pinned, device-mapped: written by a kernel whose wait gave up
@@ -497,3 +594,14 @@ int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* t
 }
 
 }  // namespace haste
+
+#ifdef HASTE_TRACE
+extern "C" int haste_dbg_trace_dump(long long* out, int* counts) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, haste::s100::g_trace, sizeof(long long) * 4 * 2048 * 2);
+  cudaMemcpyFromSymbol(counts, haste::s100::g_trace_n, sizeof(int) * 4);
+  int z[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(haste::s100::g_trace_n, z, sizeof(z));
+  return 0;
+}
+#endif
