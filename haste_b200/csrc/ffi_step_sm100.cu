@@ -49,12 +49,13 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 // barrier indices
 constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_WFULL = 2 * NXS, B_WEMPTY = B_WFULL + 2, B_ZFULL = B_WEMPTY + 2,
               B_ZEMPTY = B_ZFULL + 2, B_YFULL = B_ZEMPTY + 2, B_YEMPTY = B_YFULL + 2, B_DXFULL = B_YEMPTY + 2,
-              B_DXEMPTY = B_DXFULL + 2, B_DWFULL = B_DXEMPTY + 2, B_DWEMPTY = B_DWFULL + 1, B_MEMPTY = B_DWEMPTY + 1,
+              B_DXEMPTY = B_DXFULL + 1, B_DWFULL = B_DXEMPTY + 1, B_DWEMPTY = B_DWFULL + 2, B_MEMPTY = B_DWEMPTY + 2,
               NBAR = B_MEMPTY + 2;
 static_assert(NBAR <= 32, "barrier space");
 
 // TMEM columns
-constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
+// Z double-buffered (2 x 128), dXg single (64), dW double-buffered across groups (2 x 80)
+constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 320, TM_DW_STRIDE = 80, TM_COLS = 512;
 constexpr int NTHREADS = 512;
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
@@ -116,11 +117,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
       mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), 8);
       mbar_init(bar(B_YFULL + i), 8);  mbar_init(bar(B_YEMPTY + i), 1);
-      mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), 4);
+      mbar_init(bar(B_DWFULL + i), 1); mbar_init(bar(B_DWEMPTY + i), 4);
       mbar_init(bar(B_MEMPTY + i), 12);   // all 12 epilogue warps are done with the group's index/bias rows
     }
-    mbar_init(bar(B_DWFULL), 1);
-    mbar_init(bar(B_DWEMPTY), 4);
+    mbar_init(bar(B_DXFULL), 1);
+    mbar_init(bar(B_DXEMPTY), 4);
     mbar_fence_init();
     *abort_flag = 0;
   }
@@ -229,21 +230,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       auto backward = [&](int j, int t, int ws, int gi) {
         const int ys = j & 1, xs = j % NXS;
         mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 2, WAIT_LIMIT);
-        mbar_wait(bar(B_DXEMPTY + ys), ((j >> 1) & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
-        if (t == 0) mbar_wait(bar(B_DWEMPTY), (gi & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
+        mbar_wait(bar(B_DXEMPTY), (j & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
+        if (t == 0) mbar_wait(bar(B_DWEMPTY + (gi & 1)), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
         tc_fence_after();
         TR(1, 2000 + j);
         const uint64_t dya = D_YA + static_cast<uint64_t>(ys * (YSTAGE >> 4)), dym = D_YM + static_cast<uint64_t>(ys * (YSTAGE >> 4));
         const uint64_t dwm = D_WM + static_cast<uint64_t>(ws * (WSTAGE >> 4)), dxb = D_XB + static_cast<uint64_t>(xs * (XSTAGE >> 4));
-        const uint32_t tdx = tmem + TM_DX + ys * F;
+        const uint32_t tdx = tmem + TM_DX, tdw = tmem + TM_DW + (gi & 1) * TM_DW_STRIDE;
 #pragma unroll
         for (int ks = 0; ks < G / 16; ++ks)      // dXg[b,k] += Y[b, l-chunk] * W[l-chunk, k]
           umma_bf16(tdx, dya + static_cast<uint64_t>(((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), dwm + static_cast<uint64_t>((ks * 2048) >> 4),
                     ID_BWX, ks > 0);
-        tc_commit(bar(B_DXFULL + ys));
+        tc_commit(bar(B_DXFULL));
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks)     // dW[l,k] += Y[b-chunk, l]^T * X[k, b-chunk]
-          umma_bf16(tmem + TM_DW, dym + static_cast<uint64_t>((ks * 2048) >> 4),
+          umma_bf16(tdw, dym + static_cast<uint64_t>((ks * 2048) >> 4),
                     dxb + static_cast<uint64_t>(((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), ID_BWW, (t > 0) || (ks > 0));
         tc_commit(bar(B_YEMPTY + ys));
         tc_commit(bar(B_XEMPTY + xs));
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         }
         backward(it - 1, T - 1, ws, gi);
         tc_commit(bar(B_WEMPTY + ws));
-        tc_commit(bar(B_DWFULL));
+        tc_commit(bar(B_DWFULL + (gi & 1)));
       }
     }
   } else if (warp >= 4 && warp < 12) {
@@ -339,7 +340,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             }
             const uint32_t ym8 = (ym16 >> e8) & 0xFFu;
             float gq[8];
-            if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
+            if (LOSS == HASTE_LOSS_SQHINGE && !ragged && ym16 == 0u) {
+              // no positive among these labels (the common case): dLoss/dz = 2 max(0, 1 + z)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float m = fmaxf(1.f + z[i], 0.f);
+                gq[i] = m * gs2;
+                if (WITH_LOSS) tile_loss = fmaf(m, m, tile_loss);
+              }
+            } else if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
               // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -416,12 +425,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 11, WAIT_LIMIT);
       const int4* loc4 = reinterpret_cast<const int4*>(loc_s + ws * F);
       for (int t = 0; t < T; ++t, ++it) {
-        const int ds = it & 1;
         const int64_t b0 = static_cast<int64_t>(t) * BT;
-        mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 12, WAIT_LIMIT);
+        mbar_wait(bar(B_DXFULL), it & 1, abort_flag, a.err, 12, WAIT_LIMIT);
         tc_fence_after();
         if (bt == 0) TR(3, 1000 + it);
-        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + ds * F;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX;
         const bool live = (b0 + row < a.B) && !*abort_flag;
         float* dbase = a.dxt + b0 + row;
         // dXg[b,k] of this thread's batch row goes to dxt[loc[k], b]: for a fixed k the warp's 32 lanes hit 32
@@ -448,66 +456,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             scatter16(ra, c);
             tmem_ld_wait();
             __syncwarp();
-            if (c + 32 < F) tmem_ld16(ta + c + 32, ra);
+            if (c + 32 < F) {
+              tmem_ld16(ta + c + 32, ra);
+            } else {                                   // the whole dXg tile is in registers: hand the buffer back
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar(B_DXEMPTY));
+            }
             scatter16(rb, c + 16);
             tmem_ld_wait();
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_DXEMPTY + ds));
         if (bt == 0) TR(3, 2000 + it);
       }
       // ---- weight / bias update from the dW accumulator
-      mbar_wait(bar(B_DWFULL), gi & 1, abort_flag, a.err, 13, WAIT_LIMIT);
+      mbar_wait(bar(B_DWFULL + (gi & 1)), (gi >> 1) & 1, abort_flag, a.err, 13, WAIT_LIMIT);
       tc_fence_after();
       if (bt == 0) TR(3, 5000 + gi);
-      const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
+      const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW + (gi & 1) * TM_DW_STRIDE;
       const bool do_upd = row < rows_real && !*abort_flag;
       const int64_t l = l0 + row, gl = u.label0 + l;
       const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
       {
         __nv_bfloat16* wrow = u.w + l * F;
         const uint8_t* wsm = sm + OFF_W + ws * WSTAGE + row * 128;   // the group's W tile still holds the old weights
+        // sixteen slots (two Philox calls, interleaved by the compiler) per iteration of a real loop
 #pragma unroll 1
-        for (int c8 = 0; c8 < F / 8; ++c8) {
-          uint32_t r[8];
-          __syncwarp();                                  // the loads below are warp-collective
-          tmem_ld8(ta + c8 * 8, r);
+        for (int c16 = 0; c16 < F; c16 += 16) {
+          uint32_t r[16];
+          __syncwarp();                                  // the load below is warp-collective
+          tmem_ld16(ta + c16, r);
           tmem_ld_wait();
           if (!do_upd) continue;
-          uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
-          uint32_t* wp = reinterpret_cast<uint32_t*>(&wv);
-          uint32_t rnd[4] = {0u, 0u, 0u, 0u};          // 8 x 16 random bits, two per word
+          uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};          // 16 x 16 random bits, two per word
           if (sr) {
             if (packed) {
-              const uint4 rp = rand_packed8(u.seed, u.step, gl, c8);
-              rnd[0] = rp.x; rnd[1] = rp.y; rnd[2] = rp.z; rnd[3] = rp.w;
+              const uint4 rp0 = rand_packed8(u.seed, u.step, gl, (c16 >> 3)), rp1 = rand_packed8(u.seed, u.step, gl, (c16 >> 3) + 1);
+              rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
+              rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
             } else {
-#pragma unroll 1
-              for (int x = 0; x < 8; ++x) rnd[x >> 1] |= rand16_reference(u.seed, gl * F + c8 * 8 + x) << (16 * (x & 1));
-            }
-          }
-          uint32_t ob[4];
 #pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const float a0 = __uint_as_float(r[2 * p]), a1 = __uint_as_float(r[2 * p + 1]);
-            if (a.dw_dump != nullptr) {
-              a.dw_dump[l * F + c8 * 8 + 2 * p] = __float2bfloat16_rn(a0);
-              a.dw_dump[l * F + c8 * 8 + 2 * p + 1] = __float2bfloat16_rn(a1);
+              for (int x = 0; x < 16; x += 2)
+                rnd[x >> 1] = rand16_reference(u.seed, gl * F + c16 + x) | (rand16_reference(u.seed, gl * F + c16 + x + 1) << 16);
             }
-            // the gradient is first rounded to bf16, as the unfused kernel would store it
-            const uint32_t gp = pack_bf16x2(a0, a1);
-            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
-            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
-            float n0, n1;
-            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            const uint32_t b0 = sr ? ((__float_as_uint(n0) + (rnd[p] & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
-            const uint32_t b1 = sr ? ((__float_as_uint(n1) + (rnd[p] >> 16)) >> 16) : rn_bf16_bits(n1);
-            ob[p] = (b0 & 0xFFFFu) | (b1 << 16);
           }
-          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const int c8 = (c16 >> 3) + hf;
+            const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
+            const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
+            uint32_t ob[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
+              // the gradient is first rounded to bf16, as the unfused kernel would store it
+              const uint32_t gp = pack_bf16x2(a0, a1);
+              if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp;
+              const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
+              const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
+              float n0, n1;
+              if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+              else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+              const uint32_t rr = rnd[hf * 4 + p];
+              const uint32_t b0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
+              const uint32_t b1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
+              ob[p] = (b0 & 0xFFFFu) | (b1 << 16);
+            }
+            *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+          }
         }
       }
       uint32_t rb[8];
@@ -515,7 +531,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       if (HAS_BIAS) { tmem_ld8(ta + F, rb); tmem_ld_wait(); }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+      if (lane == 0) mbar_arrive(bar(B_DWEMPTY + (gi & 1)));
       if (HAS_BIAS && do_upd) {
         const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
         if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
