@@ -49,14 +49,15 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 // barrier indices
 constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_WFULL = 2 * NXS, B_WEMPTY = B_WFULL + 2, B_ZFULL = B_WEMPTY + 2,
               B_ZEMPTY = B_ZFULL + 2, B_YFULL = B_ZEMPTY + 2, B_YEMPTY = B_YFULL + 2, B_DXFULL = B_YEMPTY + 2,
-              B_DXEMPTY = B_DXFULL + 1, B_DWFULL = B_DXEMPTY + 1, B_DWEMPTY = B_DWFULL + 2, B_MEMPTY = B_DWEMPTY + 2,
+              B_DXEMPTY = B_DXFULL + 2, B_DWFULL = B_DXEMPTY + 2, B_DWEMPTY = B_DWFULL + 1, B_MEMPTY = B_DWEMPTY + 1,
               NBAR = B_MEMPTY + 2;
 static_assert(NBAR <= 32, "barrier space");
 
 // TMEM columns
-// Z double-buffered (2 x 128), dXg single (64), dW double-buffered across groups (2 x 80)
-constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 320, TM_DW_STRIDE = 80, TM_COLS = 512;
-constexpr int NTHREADS = 512;
+// Z double-buffered (2 x 128), dXg double-buffered (2 x 64), dW single (64 + 16)
+constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
+constexpr int NTHREADS = 768;                    // 4 control warps + 16 epilogue-A warps + 4 epilogue-B warps
+constexpr int N_EA = 16;                         // epilogue-A warps: 4 TMEM lane quarters x 4 column quarters
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
 #ifdef HASTE_TRACE
@@ -94,7 +95,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int LOSS, bool WITH_LOSS, bool HAS_BIAS>
+template <int LOSS, bool WITH_LOSS, bool HAS_BIAS, bool DEBUG>
 __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -109,19 +110,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = static_cast<int>((a.B + BT - 1) / BT);
+  // CTAs walk the batch tiles in rotated order so that, at any moment, the dX reductions of different SMs
+  // are spread over the whole dxt array instead of all landing in the same 128 batch columns
+  const int rot = static_cast<int>(blockIdx.x % static_cast<unsigned>(T));
+  auto tile_b0 = [&](int t) { int tt = t + rot; if (tt >= T) tt -= T; return static_cast<int64_t>(tt) * BT; };
 
   // ---------------- one-time setup
   if (tid == 0) {
     for (int i = 0; i < NXS; ++i) { mbar_init(bar(B_XFULL + i), 1); mbar_init(bar(B_XEMPTY + i), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
-      mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), 8);
-      mbar_init(bar(B_YFULL + i), 8);  mbar_init(bar(B_YEMPTY + i), 1);
-      mbar_init(bar(B_DWFULL + i), 1); mbar_init(bar(B_DWEMPTY + i), 4);
-      mbar_init(bar(B_MEMPTY + i), 12);   // all 12 epilogue warps are done with the group's index/bias rows
+      mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EA);
+      mbar_init(bar(B_YFULL + i), N_EA);  mbar_init(bar(B_YEMPTY + i), 2);   // both backward issuers commit
+      mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), 4);
+      mbar_init(bar(B_MEMPTY + i), N_EA + 4);   // every epilogue warp is done with the group's index/bias rows and W tile
     }
-    mbar_init(bar(B_DXFULL), 1);
-    mbar_init(bar(B_DXEMPTY), 4);
+    mbar_init(bar(B_DWFULL), 1);
+    mbar_init(bar(B_DWEMPTY), N_EA);
     mbar_fence_init();
     *abort_flag = 0;
   }
@@ -145,12 +150,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
   (void)tr_n;
   const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
 
-  if (warp == 0 || warp == 2 || warp == 3) {
+  if (warp == 0 || warp == 2) {
     // ================================================================ producers
     // The sequence of load items (per group: the W item, then one X item per batch tile) is dealt round-robin to
-    // the three producer warps; each handles one item at a time: wait for the slot, issue the copies, wait for
+    // the two producer warps; each handles one item at a time: wait for the slot, issue the copies, wait for
     // them to land, make them visible to the tensor core's proxy, signal "full".
-    const int p = (warp == 0) ? 0 : warp - 1;
+    const int p = warp >> 1;
     int item = 0, it = 0;
     auto land = [&](uint32_t full_bar) {
       cp_async_commit();
@@ -167,10 +172,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
       const int loc_lo = min(max(__ldg(lrow + lane), 0), a.D - 1);        // clamped: never addresses outside xt / dxt
       const int loc_hi = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
-      if (item % 3 == p) {
+      if ((item & 1) == p) {
         // ---- W item: weights tile, index row, bias row
-        mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
-        mbar_wait(bar(B_MEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
+        mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT, 100);
+        mbar_wait(bar(B_MEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT, 100);
         __syncwarp();
         loc_s[ws * F + lane] = loc_lo;
         loc_s[ws * F + lane + 32] = loc_hi;
@@ -191,11 +196,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       ++item;
       // ---- X items: one per batch tile
       for (int t = 0; t < T; ++t, ++it, ++item) {
-        if (item % 3 != p) continue;
+        if ((item & 1) != p) continue;
         const int xs = it % NXS;
-        mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT);
+        mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT, 100);
         __syncwarp();
-        const int64_t b0 = static_cast<int64_t>(t) * BT;
+        const int64_t b0 = tile_b0(t);
         const uint32_t xb = sbase + OFF_X + xs * XSTAGE;
         const int j = lane & 15;                     // 16-byte chunk along the batch: 8 rows each
         const bool valid = b0 + j * 8 < a.B;
@@ -211,74 +216,178 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         land(bar(B_XFULL + xs));
       }
     }
-  } else if (warp == 1) {
-    // ================================================================ MMA issuer (one thread)
+  } else if (warp == 1 || warp == 3) {
+    // ================================================================ MMA issuers (one thread each)
+    // Feeding the tensor pipe from a single thread costs more cycles per tcgen05.mma than the small (N = 64..128)
+    // products take to execute, so the work is split: warp 1 issues forward + backward-features, warp 3 issues
+    // backward-weights.  Both hang off the same mbarriers; the pipe executes in arrival order.
     if (lane == 0) {
       constexpr uint32_t ID_FWD = make_idesc(128, G, 1, 0);
       constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
       constexpr uint32_t ID_BWW = make_idesc(128, N_DW, 1, 0);
-      // Descriptors are built once; per MMA only the start-address field moves (the offsets below are in
-      // 16-byte units and never carry out of that 14-bit field because every operand lies inside the CTA's
-      // shared memory window).
+      // Descriptors are built once.  Per MMA only the start-address field (low word, 16-byte units) moves, by
+      // compile-time constants; it never carries out of its 14-bit field because every operand lies inside the
+      // CTA's shared memory window.
       const uint64_t D_XA = make_sdesc(sbase + OFF_X, XBLK, 1024);    // X tile as MN-major A   (forward)
       const uint64_t D_XB = make_sdesc(sbase + OFF_X, 16, 1024);      // X tile as K-major  B   (backward-weights)
       const uint64_t D_WB = make_sdesc(sbase + OFF_W, 16, 1024);      // W tile as K-major  B   (forward)
       const uint64_t D_WM = make_sdesc(sbase + OFF_W, WSTAGE, 1024);  // W tile as MN-major B   (backward-features)
       const uint64_t D_YA = make_sdesc(sbase + OFF_Y, 16, 1024);      // Y tile as K-major  A   (backward-features)
       const uint64_t D_YM = make_sdesc(sbase + OFF_Y, YBLK, 1024);    // Y tile as MN-major A   (backward-weights)
-      int it = 0;
-      auto backward = [&](int j, int t, int ws, int gi) {
-        const int ys = j & 1, xs = j % NXS;
-        mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 2, WAIT_LIMIT);
-        mbar_wait(bar(B_DXEMPTY), (j & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
-        if (t == 0) mbar_wait(bar(B_DWEMPTY + (gi & 1)), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
-        tc_fence_after();
-        TR(1, 2000 + j);
-        const uint64_t dya = D_YA + static_cast<uint64_t>(ys * (YSTAGE >> 4)), dym = D_YM + static_cast<uint64_t>(ys * (YSTAGE >> 4));
-        const uint64_t dwm = D_WM + static_cast<uint64_t>(ws * (WSTAGE >> 4)), dxb = D_XB + static_cast<uint64_t>(xs * (XSTAGE >> 4));
-        const uint32_t tdx = tmem + TM_DX, tdw = tmem + TM_DW + (gi & 1) * TM_DW_STRIDE;
-#pragma unroll
-        for (int ks = 0; ks < G / 16; ++ks)      // dXg[b,k] += Y[b, l-chunk] * W[l-chunk, k]
-          umma_bf16(tdx, dya + static_cast<uint64_t>(((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), dwm + static_cast<uint64_t>((ks * 2048) >> 4),
-                    ID_BWX, ks > 0);
-        tc_commit(bar(B_DXFULL));
-#pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks)     // dW[l,k] += Y[b-chunk, l]^T * X[k, b-chunk]
-          umma_bf16(tdw, dym + static_cast<uint64_t>((ks * 2048) >> 4),
-                    dxb + static_cast<uint64_t>(((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), ID_BWW, (t > 0) || (ks > 0));
-        tc_commit(bar(B_YEMPTY + ys));
-        tc_commit(bar(B_XEMPTY + xs));
-        TR(1, 3000 + j);
-      };
-      for (int gi = 0; gi < n_my_groups; ++gi) {
-        const int ws = gi & 1;
-        mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 5, WAIT_LIMIT);
-        for (int t = 0; t < T; ++t, ++it) {
-          const int xs = it % NXS, zs = it & 1;
-          mbar_wait(bar(B_XFULL + xs), (it / NXS) & 1, abort_flag, a.err, 6, WAIT_LIMIT);
-          mbar_wait(bar(B_ZEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 7, WAIT_LIMIT);
+      if (warp == 1) {
+        // ---------------- forward + backward-features
+        const uint32_t xa_lo = static_cast<uint32_t>(D_XA), xa_hi = static_cast<uint32_t>(D_XA >> 32);
+        const uint32_t wb_lo = static_cast<uint32_t>(D_WB), wb_hi = static_cast<uint32_t>(D_WB >> 32);
+        const uint32_t wm_lo = static_cast<uint32_t>(D_WM), wm_hi = static_cast<uint32_t>(D_WM >> 32);
+        const uint32_t ya_lo = static_cast<uint32_t>(D_YA), ya_hi = static_cast<uint32_t>(D_YA >> 32);
+        const uint32_t id_fwd = ID_FWD, id_bwx = ID_BWX;
+        int it = 0, xs = 0, xph = 0;
+        auto backward_x = [&](int j, int ws) {
+          const int ys = j & 1;
+          mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 2, WAIT_LIMIT);
+          mbar_wait(bar(B_DXEMPTY + ys), ((j >> 1) & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
           tc_fence_after();
-          TR(1, 1000 + it);
-          const uint64_t dxa = D_XA + static_cast<uint64_t>(xs * (XSTAGE >> 4)), dwb = D_WB + static_cast<uint64_t>(ws * (WSTAGE >> 4));
-          const uint32_t tz = tmem + TM_Z + zs * G;
+          TR(1, 2000 + j);
+          const uint32_t ya = ya_lo + (ys ? (YSTAGE >> 4) : 0u), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
+          const uint32_t tdx = tmem + TM_DX + (ys ? F : 0);
+          // dXg[b,k] = sum over label chunks of Y[b, l-chunk] * W[l-chunk, k]
+          umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
 #pragma unroll
-          for (int ks = 0; ks < F / 16; ++ks)    // Z[b,l] += X[k-chunk, b]^T * W[l, k-chunk]
-            umma_bf16(tz, dxa + static_cast<uint64_t>((ks * 2048) >> 4), dwb + static_cast<uint64_t>((ks * 32) >> 4), ID_FWD, ks > 0);
-          tc_commit(bar(B_ZFULL + zs));
-          if (t > 0) backward(it - 1, t - 1, ws, gi);
+          for (int ks = 1; ks < G / 16; ++ks)
+            umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
+          tc_commit(bar(B_DXFULL + ys));
+          tc_commit(bar(B_YEMPTY + ys));
+          TR(1, 3000 + j);
+        };
+        for (int gi = 0; gi < n_my_groups; ++gi) {
+          const int ws = gi & 1;
+          mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 5, WAIT_LIMIT);
+          for (int t = 0; t < T; ++t, ++it) {
+            const int zs = it & 1;
+            mbar_wait(bar(B_XFULL + xs), xph, abort_flag, a.err, 6, WAIT_LIMIT);
+            mbar_wait(bar(B_ZEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 7, WAIT_LIMIT);
+            tc_fence_after();
+            TR(1, 1000 + it);
+            const uint32_t xa = xa_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4), wb = wb_lo + (ws ? (WSTAGE >> 4) : 0u);
+            const uint32_t tz = tmem + TM_Z + (zs ? G : 0);
+            // Z[b,l] = sum over slot chunks of X[k-chunk, b]^T * W[l, k-chunk]
+            umma_bf16_lohi<false>(tz, xa, xa_hi, wb, wb_hi, id_fwd);
+#pragma unroll
+            for (int ks = 1; ks < F / 16; ++ks)
+              umma_bf16_lohi<true>(tz, xa + ((ks * 2048) >> 4), xa_hi, wb + ((ks * 32) >> 4), wb_hi, id_fwd);
+            tc_commit(bar(B_ZFULL + zs));
+            if (++xs == NXS) { xs = 0; xph ^= 1; }
+            if (t > 0) backward_x(it - 1, ws);
+          }
+          backward_x(it - 1, ws);
+          tc_commit(bar(B_WEMPTY + ws));          // every product that reads this group's W tile has been issued
         }
-        backward(it - 1, T - 1, ws, gi);
-        tc_commit(bar(B_WEMPTY + ws));
-        tc_commit(bar(B_DWFULL + (gi & 1)));
+      } else {
+        // ---------------- backward-weights
+        const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
+        const uint32_t ym_lo = static_cast<uint32_t>(D_YM), ym_hi = static_cast<uint32_t>(D_YM >> 32);
+        const uint32_t id_bww = ID_BWW;
+        int j = 0, xs = 0;
+        for (int gi = 0; gi < n_my_groups; ++gi) {
+          const uint32_t tdw = tmem + TM_DW;
+          mbar_wait(bar(B_DWEMPTY), (gi & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
+          for (int t = 0; t < T; ++t, ++j) {
+            const int ys = j & 1;
+            // Y(t) complete implies forward(t) complete, so the tile's X slot is loaded as well
+            mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 14, WAIT_LIMIT);
+            tc_fence_after();
+            const uint32_t ym = ym_lo + (ys ? (YSTAGE >> 4) : 0u), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
+            // dW[l,k] += sum over batch chunks of Y[b-chunk, l]^T * X[k, b-chunk]
+            umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
+#pragma unroll
+            for (int ks = 1; ks < BT / 16; ++ks)
+              umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
+            tc_commit(bar(B_YEMPTY + ys));
+            tc_commit(bar(B_XEMPTY + xs));
+            if (++xs == NXS) xs = 0;
+          }
+          tc_commit(bar(B_DWFULL));
+        }
       }
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < 4 + N_EA) {
     // ================================================================ epilogue A: Z -> dY
-    const int ea = warp - 4, q = ea & 3, h = ea >> 2;
+    const int ea = warp - 4, q = ea & 3, cq = ea >> 2;   // TMEM lane quarter, column quarter (32 labels each)
     const int row = q * 32 + lane;               // batch row inside the tile == TMEM lane
-    const int et = tid - 128;                    // 0..255
+    const int et = tid - 128;                    // 0..511
     float loss_acc = 0.f;
     int it = 0;
+    // Weight / bias update of one finished group from its dW accumulator: warp (q, cq) owns label rows
+    // q*32..q*32+31 and slots cq*16..cq*16+15 (two Philox calls in the packed stream).  Runs one batch tile
+    // behind the group's own tiles so the accumulator is certainly complete and the tensor core is not held up.
+    auto update_group = [&](int gu) {
+      const int gg = blockIdx.x + gu * gridDim.x;
+      const int wsu = gu & 1;
+      const int64_t l0 = static_cast<int64_t>(gg) * G;
+      const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
+      mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
+      tc_fence_after();
+      const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
+      uint32_t r[16], rb[8];
+      __syncwarp();
+      tmem_ld16(tdw + cq * 16, r);
+      if (HAS_BIAS && cq == 0) tmem_ld8(tdw + F, rb);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+      if (row < rows_real_u && !*abort_flag) {
+        const int64_t l = l0 + row, gl = u.label0 + l;
+        const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
+        __nv_bfloat16* wrow = u.w + l * F;
+        const uint8_t* wsm = sm + OFF_W + wsu * WSTAGE + row * 128;   // the group's W tile still holds the old weights
+        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
+        if (sr) {
+          if (packed) {
+            const uint4 rp0 = rand_packed8(u.seed, u.step, gl, cq * 2), rp1 = rand_packed8(u.seed, u.step, gl, cq * 2 + 1);
+            rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
+            rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
+          } else {
+#pragma unroll
+            for (int x = 0; x < 16; x += 2)
+              rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + cq * 16 + x) | (rand16_reference_call(u.seed, gl * F + cq * 16 + x + 1) << 16);
+          }
+        }
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int c8 = cq * 2 + hf;
+          const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
+          const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
+          uint32_t ob[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
+            // the gradient is first rounded to bf16, as the unfused kernel would store it
+            const uint32_t gp = pack_bf16x2(a0, a1);
+            if (DEBUG) { if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp; }
+            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
+            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
+            float n0, n1;
+            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            const uint32_t rr = rnd[hf * 4 + p];
+            const uint32_t o0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
+            const uint32_t o1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
+            ob[p] = (o0 & 0xFFFFu) | (o1 << 16);
+          }
+          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+        if (HAS_BIAS && cq == 0) {
+          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
+          if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
+          uint32_t r16 = 0;
+          if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
+          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / index row / bias row
+    };
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
@@ -288,20 +397,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 8, WAIT_LIMIT);   // bias_s of this group is in place
       for (int t = 0; t < T; ++t, ++it) {
         const int zs = it & 1;
-        const int64_t b0 = static_cast<int64_t>(t) * BT;
-        uint32_t ym[2] = {0u, 0u};
+        const int64_t b0 = tile_b0(t);
+        uint32_t ym32 = 0u;
         if (has_t) {
           uint32_t* yb = ybits + (it & 1) * BT * 4;
-          yb[et * 2] = 0u; yb[et * 2 + 1] = 0u;
-          named_bar_sync(1, 256);
-          for (int i = t_beg + et; i < t_end; i += 256) {
+          yb[et] = 0u;
+          named_bar_sync(1, N_EA * 32);
+          for (int i = t_beg + et; i < t_end; i += N_EA * 32) {
             const uint32_t e = __ldg(a.tgt_ent + i);
             const int64_t rb = static_cast<int64_t>(e >> 8) - b0;
             const int c = e & 0xFF;
             if (rb >= 0 && rb < BT && c < G) atomicOr(&yb[rb * 4 + (c >> 5)], 1u << (c & 31));
           }
-          named_bar_sync(1, 256);
-          ym[0] = yb[row * 4 + h * 2]; ym[1] = yb[row * 4 + h * 2 + 1];
+          named_bar_sync(1, N_EA * 32);
+          ym32 = yb[row * 4 + cq];
         }
         const bool row_valid = b0 + row < a.B;
         const float gs = row_valid ? a.grad_scale : 0.f;
@@ -310,17 +419,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         mbar_wait(bar(B_YEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
         tc_fence_after();
         if (ea == 0 && lane == 0) TR(2, 2000 + it);
-        uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + h * YBLK + row * 128;
-        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + h * 64;
-        const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + h * 64);
+        const int col0 = cq * 32;                                  // first label column of this warp
+        uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + (cq >> 1) * YBLK + row * 128;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + col0;
+        const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + col0);
         const float gs2 = 2.f * gs;
-        const bool ragged = h * 64 + 64 > rows_real;   // only the last group of the layer can be ragged
-        const uint64_t ym64 = static_cast<uint64_t>(ym[0]) | (static_cast<uint64_t>(ym[1]) << 32);
-        float tile_loss = 0.f;
-        // 16-column chunks, software-pipelined (the TMEM load of the next chunk is in flight while this one is
-        // processed) in a real loop: four roles share each scheduler's instruction cache, so code stays small.
-        auto process16 = [&](const uint32_t (&r)[16], int c16) {
-          const uint32_t ym16 = static_cast<uint32_t>(ym64 >> c16) & 0xFFFFu;
+        const float inv_gs2_sq = row_valid ? 1.f / (gs2 * gs2) : 0.f;
+        const bool ragged = col0 + 32 > rows_real;     // only the last group of the layer can be ragged
+        float tile_loss = 0.f, fast_loss = 0.f;
+        // two 16-column chunks in a real loop (small code: four roles share each scheduler's instruction cache);
+        // with four epilogue-A warps per scheduler the TMEM load latency is covered by the other warps
+#pragma unroll 1
+        for (int c16 = 0; c16 < 32; c16 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld16(ta + c16, r);
+          tmem_ld_wait();
+          const uint32_t ym16 = (ym32 >> c16) & 0xFFFFu;
 #pragma unroll
           for (int e8 = 0; e8 < 16; e8 += 8) {
             float z[8];
@@ -341,12 +456,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             const uint32_t ym8 = (ym16 >> e8) & 0xFFu;
             float gq[8];
             if (LOSS == HASTE_LOSS_SQHINGE && !ragged && ym16 == 0u) {
-              // no positive among these labels (the common case): dLoss/dz = 2 max(0, 1 + z)
+              // no positive among these labels (the common case): dLoss/dz = 2 s max(0, 1 + z) with s = grad_scale,
+              // evaluated as max(0, fma(2s, z, 2s)); 1 + z is exact in fp32 for a bf16 z (down to |z| ~ 2^-16), so
+              // this is the same single rounding as (1 + z) * 2s.  The loss term max(0,1+z)^2 is accumulated as
+              // g^2 and rescaled by 1/(2s)^2 once per tile.
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float m = fmaxf(1.f + z[i], 0.f);
-                gq[i] = m * gs2;
-                if (WITH_LOSS) tile_loss = fmaf(m, m, tile_loss);
+                gq[i] = fmaxf(fmaf(gs2, z[i], gs2), 0.f);
+                if (WITH_LOSS) fast_loss = fmaf(gq[i], gq[i], fast_loss);
               }
             } else if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
               // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
@@ -362,184 +479,89 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
               for (int i = 0; i < 8; ++i) {
                 float la = 0.f;
                 float gl = loss_grad<LOSS, WITH_LOSS>(z[i], (ym8 >> i) & 1u, la);
-                if (ragged && h * 64 + c16 + e8 + i >= rows_real) { gl = 0.f; la = 0.f; }
+                if (ragged && col0 + c16 + e8 + i >= rows_real) { gl = 0.f; la = 0.f; }
                 if (WITH_LOSS) tile_loss += la;
                 gq[i] = gl * gs;
               }
             }
-            if (a.z_dump != nullptr && row_valid) {
-              uint16_t* zd = reinterpret_cast<uint16_t*>(a.z_dump) + (b0 + row) * a.ldz + static_cast<int64_t>(g) * G + h * 64 + c16 + e8;
+            if (DEBUG) {
+              if (a.z_dump != nullptr && row_valid) {
+                uint16_t* zd = reinterpret_cast<uint16_t*>(a.z_dump) + (b0 + row) * a.ldz + static_cast<int64_t>(g) * G + col0 + c16 + e8;
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (h * 64 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>((i & 1) ? (zp[i >> 1] >> 16) : (zp[i >> 1] & 0xFFFFu));
+                for (int i = 0; i < 8; ++i)
+                  if (col0 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>((i & 1) ? (zp[i >> 1] >> 16) : (zp[i >> 1] & 0xFFFFu));
+              }
             }
-            *reinterpret_cast<uint4*>(ytile + ((((c16 + e8) >> 3) ^ (row & 7)) << 4)) =
+            const int chunk = ((col0 & 63) + c16 + e8) >> 3;       // 16-byte chunk inside the 128-byte row of this block
+            *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) =
                 make_uint4(pack_bf16x2(gq[0], gq[1]), pack_bf16x2(gq[2], gq[3]), pack_bf16x2(gq[4], gq[5]), pack_bf16x2(gq[6], gq[7]));
-          }
-        };
-        {
-          uint32_t ra[16], rb[16];
-          tmem_ld16(ta, ra);
-          tmem_ld_wait();
-#pragma unroll 1
-          for (int c = 0; c < 64; c += 32) {
-            __syncwarp();
-            tmem_ld16(ta + c + 16, rb);
-            process16(ra, c);
-            tmem_ld_wait();
-            __syncwarp();
-            if (c + 32 < 64) tmem_ld16(ta + c + 32, ra);
-            process16(rb, c + 16);
-            tmem_ld_wait();
           }
         }
         tc_fence_before();                             // this warp's half of the Z stage has been read
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
-        if (WITH_LOSS) loss_acc += row_valid ? tile_loss : 0.f;
+        if (WITH_LOSS && row_valid) loss_acc += tile_loss + fast_loss * inv_gs2_sq;
         if (ea == 0 && lane == 0) TR(2, 2700 + it);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_YFULL + zs));
         if (ea == 0 && lane == 0) TR(2, 3000 + it);
+        if (t == 0 && gi > 0) update_group(gi - 1);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));
     }
+    if (n_my_groups > 0) update_group(n_my_groups - 1);
     if (WITH_LOSS) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) loss_acc += __shfl_xor_sync(0xffffffffu, loss_acc, o);
       if (lane == 0 && !*abort_flag) atomicAdd(a.loss, loss_acc * a.grad_scale);
     }
-  } else if (warp >= 12) {
-    // ================================================================ epilogue B: dXg scatter, weight update
+  } else if (warp >= 4 + N_EA) {
+    // ================================================================ epilogue B: dXg scatter
     const int q = warp & 3;
-    const int row = q * 32 + lane;               // TMEM lane: batch row (dXg) or label row (dW)
-    const int bt = tid - 384;                    // 0..127
+    const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
+    const int bt = tid - (4 + N_EA) * 32;        // 0..127
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
-      const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
-      const int64_t l0 = static_cast<int64_t>(g) * G;
-      const int rows_real = static_cast<int>(imin64(G, a.L - l0));
-      mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 11, WAIT_LIMIT);
+      mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 11, WAIT_LIMIT);   // loc_s of this group is in place
       const int4* loc4 = reinterpret_cast<const int4*>(loc_s + ws * F);
       for (int t = 0; t < T; ++t, ++it) {
-        const int64_t b0 = static_cast<int64_t>(t) * BT;
-        mbar_wait(bar(B_DXFULL), it & 1, abort_flag, a.err, 12, WAIT_LIMIT);
+        const int64_t b0 = tile_b0(t);
+        const int ds = it & 1;
+        mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 12, WAIT_LIMIT);
         tc_fence_after();
         if (bt == 0) TR(3, 1000 + it);
-        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX;
-        const bool live = (b0 + row < a.B) && !*abort_flag;
-        float* dbase = a.dxt + b0 + row;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + (ds ? F : 0);
+        uint32_t r0[32], r1[32];
+        tmem_ld32(ta, r0);
+        tmem_ld32(ta + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before();                         // the whole dXg tile is in registers: hand the buffer back at once
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_DXEMPTY + ds));
         // dXg[b,k] of this thread's batch row goes to dxt[loc[k], b]: for a fixed k the warp's 32 lanes hit 32
         // consecutive floats, so each red below is one 128-byte transaction
-        auto scatter16 = [&](const uint32_t (&r)[16], int c16) {
-          if (!live) return;
+        if ((b0 + row < a.B) && !*abort_flag) {
+          float* dbase = a.dxt + b0 + row;
 #pragma unroll
-          for (int k4 = 0; k4 < 16; k4 += 4) {
-            const int4 lc = loc4[(c16 + k4) >> 2];
-            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r[k4 + 0]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r[k4 + 1]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r[k4 + 2]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r[k4 + 3]));
+          for (int k4 = 0; k4 < 32; k4 += 4) {
+            const int4 lc = loc4[k4 >> 2];
+            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r0[k4 + 0]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r0[k4 + 1]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r0[k4 + 2]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r0[k4 + 3]));
           }
-        };
-        {
-          uint32_t ra[16], rb[16];
-          tmem_ld16(ta, ra);
-          tmem_ld_wait();
-#pragma unroll 1
-          for (int c = 0; c < F; c += 32) {
-            __syncwarp();
-            tmem_ld16(ta + c + 16, rb);
-            scatter16(ra, c);
-            tmem_ld_wait();
-            __syncwarp();
-            if (c + 32 < F) {
-              tmem_ld16(ta + c + 32, ra);
-            } else {                                   // the whole dXg tile is in registers: hand the buffer back
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(bar(B_DXEMPTY));
-            }
-            scatter16(rb, c + 16);
-            tmem_ld_wait();
+#pragma unroll
+          for (int k4 = 0; k4 < 32; k4 += 4) {
+            const int4 lc = loc4[8 + (k4 >> 2)];
+            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r1[k4 + 0]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r1[k4 + 1]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r1[k4 + 2]));
+            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r1[k4 + 3]));
           }
         }
         if (bt == 0) TR(3, 2000 + it);
       }
-      // ---- weight / bias update from the dW accumulator
-      mbar_wait(bar(B_DWFULL + (gi & 1)), (gi >> 1) & 1, abort_flag, a.err, 13, WAIT_LIMIT);
-      tc_fence_after();
-      if (bt == 0) TR(3, 5000 + gi);
-      const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW + (gi & 1) * TM_DW_STRIDE;
-      const bool do_upd = row < rows_real && !*abort_flag;
-      const int64_t l = l0 + row, gl = u.label0 + l;
-      const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
-      {
-        __nv_bfloat16* wrow = u.w + l * F;
-        const uint8_t* wsm = sm + OFF_W + ws * WSTAGE + row * 128;   // the group's W tile still holds the old weights
-        // sixteen slots (two Philox calls, interleaved by the compiler) per iteration of a real loop
-#pragma unroll 1
-        for (int c16 = 0; c16 < F; c16 += 16) {
-          uint32_t r[16];
-          __syncwarp();                                  // the load below is warp-collective
-          tmem_ld16(ta + c16, r);
-          tmem_ld_wait();
-          if (!do_upd) continue;
-          uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};          // 16 x 16 random bits, two per word
-          if (sr) {
-            if (packed) {
-              const uint4 rp0 = rand_packed8(u.seed, u.step, gl, (c16 >> 3)), rp1 = rand_packed8(u.seed, u.step, gl, (c16 >> 3) + 1);
-              rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
-              rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
-            } else {
-#pragma unroll
-              for (int x = 0; x < 16; x += 2)
-                rnd[x >> 1] = rand16_reference(u.seed, gl * F + c16 + x) | (rand16_reference(u.seed, gl * F + c16 + x + 1) << 16);
-            }
-          }
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const int c8 = (c16 >> 3) + hf;
-            const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
-            const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
-            uint32_t ob[4];
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
-              // the gradient is first rounded to bf16, as the unfused kernel would store it
-              const uint32_t gp = pack_bf16x2(a0, a1);
-              if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp;
-              const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
-              const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
-              float n0, n1;
-              if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-              else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-              const uint32_t rr = rnd[hf * 4 + p];
-              const uint32_t b0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
-              const uint32_t b1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
-              ob[p] = (b0 & 0xFFFFu) | (b1 << 16);
-            }
-            *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-          }
-        }
-      }
-      uint32_t rb[8];
-      __syncwarp();
-      if (HAS_BIAS) { tmem_ld8(ta + F, rb); tmem_ld_wait(); }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DWEMPTY + (gi & 1)));
-      if (HAS_BIAS && do_upd) {
-        const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
-        if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
-        uint32_t r16 = 0;
-        if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
-        u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
-      }
-      if (bt == 0) TR(3, 6000 + gi);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));
     }
@@ -591,20 +613,25 @@ int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* t
   const int grid = a.NG < sms ? a.NG : sms;
   const bool wl = (u.flags & HASTE_F_LOSS) && loss != nullptr;
   const bool hb = u.bias != nullptr;
-#define HASTE_S100_LAUNCH(LK, WL, HB)                                                                              \
+#define HASTE_S100_LAUNCH(LK, WL, HB, DBG)                                                                         \
   {                                                                                                                \
-    auto k = ffi_train_step_sm100_kernel<LK, WL, HB>;                                                              \
+    auto k = ffi_train_step_sm100_kernel<LK, WL, HB, DBG>;                                                         \
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);               \
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));         \
     k<<<grid, NTHREADS, SMEM_BYTES, st>>>(a, u);                                                                    \
   }
-  if (loss_kind == HASTE_LOSS_BCE) {
-    if (wl) { if (hb) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, true, true) else HASTE_S100_LAUNCH(HASTE_LOSS_BCE, true, false) }
-    else    { if (hb) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, false, true) else HASTE_S100_LAUNCH(HASTE_LOSS_BCE, false, false) }
+#define HASTE_S100_BY_LOSS(WL, HB, DBG)                                                                            \
+  { if (loss_kind == HASTE_LOSS_BCE) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, WL, HB, DBG) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, WL, HB, DBG) }
+  if (dump != nullptr) {
+    // the debug variants always accumulate the loss
+    if (loss == nullptr) return fail(HASTE_ERR_BAD_ARG, "debug step needs a loss pointer");
+    if (hb) HASTE_S100_BY_LOSS(true, true, true) else HASTE_S100_BY_LOSS(true, false, true)
+  } else if (wl) {
+    if (hb) HASTE_S100_BY_LOSS(true, true, false) else HASTE_S100_BY_LOSS(true, false, false)
   } else {
-    if (wl) { if (hb) HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, true, true) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, true, false) }
-    else    { if (hb) HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, false, true) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, false, false) }
+    if (hb) HASTE_S100_BY_LOSS(false, true, false) else HASTE_S100_BY_LOSS(false, false, false)
   }
+#undef HASTE_S100_BY_LOSS
 #undef HASTE_S100_LAUNCH
   return check_launch("ffi_train_step_sm100_kernel");
 }
