@@ -223,6 +223,49 @@ int launch_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64
   return check_launch("targets_bucket");
 }
 
+// ---------------------------------------------------------------- target bucketing without any allocation
+// Scratch for haste_targets_bucket_noalloc: one int32 counter per label group, resident in every GPU that loads
+// this library (256 KiB) until the process exits.
+constexpr int64_t NOALLOC_MAX_GROUPS = 65536;
+static __device__ __align__(256) int32_t g_bucket_scratch[NOALLOC_MAX_GROUPS];
+
+// In host code `g_bucket_scratch` is only a handle for the device symbol, not a device address, so the address
+// is looked up once per device (with that device current) and cached.
+static int32_t* noalloc_scratch_ptr(int* rc) {
+  constexpr int MAX_DEV = 64;
+  static int32_t* cache[MAX_DEV] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
+    *rc = fail(HASTE_ERR_LAUNCH, "haste_targets_bucket_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    return nullptr;
+  }
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_bucket_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *rc = fail(HASTE_ERR_LAUNCH, "haste_targets_bucket_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = static_cast<int32_t*>(p);
+  }
+  *rc = HASTE_OK;
+  return cache[dev];
+}
+
+int launch_targets_bucket_noalloc(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G, int32_t* ptr, uint32_t* ent,
+                                  cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  if (NG > NOALLOC_MAX_GROUPS)
+    return fail(HASTE_ERR_TOO_LARGE, "haste_targets_bucket_noalloc: %lld label groups exceed the built-in scratch of %lld groups; "
+                "use haste_targets_bucket with caller-provided scratch", (long long)NG, (long long)NOALLOC_MAX_GROUPS);
+  int rc = HASTE_OK;
+  int32_t* scratch = noalloc_scratch_ptr(&rc);
+  if (scratch == nullptr) return rc;
+  // the counters keep the previous call's values: launch_targets_bucket clears the NG it uses before counting
+  return launch_targets_bucket(coo, nnz, label0, L, G, ptr, ent, scratch, st);
+}
+
 int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st) {
   int* bad = nullptr;
   cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&bad), sizeof(int), st);

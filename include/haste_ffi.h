@@ -98,6 +98,24 @@ int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, voi
 int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G,
                          int32_t* tgt_ptr, uint32_t* tgt_ent, int32_t* scratch, haste_stream_t stream);
 
+/* haste_targets_bucket for callers that must not allocate device memory.  (No counterpart in the reference.)
+ *
+ * Who needs it: a host that gave all device memory to its own arena at start-up and has nothing left to hand
+ * out, a step loop that cannot afford the device-wide synchronisation a cudaMalloc/cudaFree may cause, or a
+ * plugin that only receives raw pointers and has no allocator of the hosting framework within reach.  Such
+ * callers cannot provide the `scratch` array of haste_targets_bucket; here it lives in a fixed 256 KiB array
+ * inside the library (one int32 per label group) that every GPU which loads the library holds until exit.
+ *
+ * Same inputs, outputs and result as haste_targets_bucket.  Limits and rules:
+ *   - at most 65536 label groups (ceil(L/G)); more returns HASTE_ERR_TOO_LARGE — use haste_targets_bucket then;
+ *   - the first call on each device looks up the array's device address (the device must be current, as for
+ *     every call); make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: two calls that may overlap on the GPU (different streams)
+ *     race — order them.  The array keeps the last call's contents; each call clears the part it uses itself;
+ *   - calls no cudaMalloc / cudaFree nor any allocating library routine. */
+int haste_targets_bucket_noalloc(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G,
+                                 int32_t* tgt_ptr, uint32_t* tgt_ent, haste_stream_t stream);
+
 /* Fused training step of the layer for one label shard:
  *   z = forward; dy = grad_scale * dLoss/dz (BCE-with-logits sum, or squared hinge);
  *   dxt += backward-features; w,bias <- SGD(+wd)(+momentum) + stochastic rounding of backward-weights.
