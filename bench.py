@@ -226,7 +226,7 @@ def run_ours(args):
             "gpu_launches": 5 * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,
                          "kernel": "fused train step", "kernel_ms": kern_ms_avg, "peak_source": peaks["source"] + " burst bf16"},
             "wall_s_timed_region": t_wall,
         }
@@ -294,6 +294,56 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_aux(args):
+    """Device times of the other kernels of the path on the chosen workload (one GPU), each against the roofline
+    that bounds it: the unfused forward / backward kernels and the streaming kernels are HBM-bound, so the figure
+    is algorithmic bytes / time against the measured copy bandwidth.  Prints one JSON line per kernel."""
+    from haste_b200 import synth, ffi as hffi
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    c = synth.WORKLOADS[args.workload]
+    B, D, L, F, G = c["B"], c["D"], c["L"], c["F"], c["G"]
+    loc, W, bias = synth.make_layer(D, L, F, G, seed=42)
+    X, _ = synth.make_batch(B, D, L, c["avg_pos"], c["zipf"], c["x"], seed=1000)
+    loc, W, bias, X = loc.to(dev), W.to(dev), bias.to(dev), X.to(dev)
+    xt = hffi.transpose_bf16(X)
+    NG = (L + G - 1) // G
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timeit(fn, n=10):
+        ts = []
+        for i in range(n + 3):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                ts.append(a.elapsed_time(b))
+        return statistics.mean(ts)
+
+    z = hffi.forward(loc, xt, W, bias, G)
+    dy = torch.randn(B, L, device=dev).to(torch.bfloat16)
+    g = torch.randn(L, F, device=dev).to(torch.bfloat16)
+    mom = torch.zeros(L, F, device=dev)
+    w2 = W.clone()
+    rows = [
+        ("ffi_forward (unfused, writes Z)", lambda: hffi.forward(loc, xt, W, bias, G), 2 * B * L + 2 * L * F + 4 * NG * F),
+        ("ffi_backward_features (unfused, reads dY)", lambda: hffi.backward_features(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
+        ("ffi_backward_weights (unfused, reads dY, writes dW)", lambda: hffi.backward_weights(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
+        ("ffi_bww_sr_sgd (backward-weights + SGD/SR, no dW)", lambda: hffi.bww_sr_sgd(xt, loc, dy, w2, None, None, None, G, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 2 * B * L + 4 * L * F + 4 * NG * F),
+        ("sgd_sr_update packed stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 6 * L * F),
+        ("sgd_sr_update reference stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="reference")), 6 * L * F),
+        ("sgd_sr_update packed + momentum", lambda: hffi.sgd_sr_update(w2, g, mom, 0, LR, WD, 0.9, SEED, 1, hffi.make_flags(rng="packed")), 14 * L * F),
+        ("rewire fraction 0.15, unused regrow, zero init, regroup", lambda: hffi.rewire(w2, loc, None, D, G, 0, 1, 0.0, int(F * 0.15), 1, 0, True, SEED, 1, None), 4 * L * F + 8 * NG * F),
+    ]
+    for name, fn, nbytes in rows:
+        ms = timeit(fn)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"kernel": name, "workload": args.workload, "ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                          "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "bound": "hbm"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -302,9 +352,12 @@ def main():
     ap.add_argument("--workload", default="c3")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--aux", action="store_true", help="time the unfused and streaming kernels instead of the train step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.aux:
+        run_aux(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
