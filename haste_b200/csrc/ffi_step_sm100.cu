@@ -465,6 +465,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
                 gq[i] = fmaxf(fmaf(gs2, z[i], gs2), 0.f);
                 if (WITH_LOSS) fast_loss = fmaf(gq[i], gq[i], fast_loss);
               }
+            } else if (LOSS == HASTE_LOSS_BCE && !ragged && ym16 == 0u) {
+              // no positive among these labels: dLoss/dz = sigmoid(z) = 0.5 + 0.5 tanh(z/2) (one MUFU op);
+              // loss term softplus(z) = max(z,0) - ln(max(sigmoid, 1 - sigmoid)) = max(z,0) - ln(0.5 + 0.5 |tanh(z/2)|),
+              // whose logarithm argument stays in [0.5, 1] (no cancellation for large |z|)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float th;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z[i]));
+                gq[i] = fmaf(0.5f, th, 0.5f) * gs;
+                if (WITH_LOSS) tile_loss += fmaxf(z[i], 0.f) - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
+              }
             } else if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
               // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
 #pragma unroll
