@@ -399,7 +399,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         const int zs = it & 1;
         const int64_t b0 = tile_b0(t);
         uint32_t ym32 = 0u;
-        if (has_t) {
+        if (has_t && t_end - t_beg <= 8) {
+          // Few targets in this group (the common case): each thread picks the bits of its own row and 32 label
+          // columns straight from the entry list — no shared bitmap, no barrier between the epilogue warps.
+          const uint32_t rowkey = static_cast<uint32_t>(b0 + row);
+          for (int i = t_beg; i < t_end; ++i) {
+            const uint32_t e = __ldg(a.tgt_ent + i);
+            const uint32_t c = (e & 0xFFu) - static_cast<uint32_t>(cq * 32);
+            if ((e >> 8) == rowkey && c < 32u) ym32 |= 1u << c;
+          }
+        } else if (has_t) {
           uint32_t* yb = ybits + (it & 1) * BT * 4;
           yb[et] = 0u;
           named_bar_sync(1, N_EA * 32);
