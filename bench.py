@@ -223,7 +223,7 @@ def run_ours(args):
                        "layer_tflops": flops / (ms_per_step * 1e-3) / 1e12},
             "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": 2 * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,

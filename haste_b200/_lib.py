@@ -26,6 +26,7 @@ SIGNATURES = {
     "haste_ffi_backward_weights": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, P],
     "haste_ffi_bww_sr_sgd": [P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F32, F32, F32, U64, U32, U32, P],
     "haste_targets_bucket": [P, I64, I64, I64, I64, P, P, P, P],
+    "haste_ffi_step_prepare": [P, P, P, P, P, I64, I64, I64, I64, P, P, I64, I64, P],
     "haste_targets_bucket_noalloc": [P, I64, I64, I64, I64, P, P, P],
     "haste_ffi_train_step": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64,
                              U32, U32, P],

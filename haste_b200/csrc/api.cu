@@ -134,6 +134,15 @@ int haste_targets_bucket_noalloc(const int32_t* coo, int64_t nnz, int64_t label0
   return launch_targets_bucket_noalloc(coo, nnz, label0, L, G, tgt_ptr, tgt_ent, static_cast<cudaStream_t>(stream));
 }
 
+int haste_ffi_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz, int64_t label0, int64_t L,
+                           int64_t G, int32_t* tgt_ptr, uint32_t* tgt_ent, int64_t B, int64_t D, haste_stream_t stream) {
+  const char* who = "haste_ffi_step_prepare";
+  REQUIRE_PTR(x, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(dxt, who); REQUIRE_PTR(tgt_ptr, who);
+  if (nnz < 0 || L < 1 || G < 1 || G > 256 || B < 1 || D < 1) return fail(HASTE_ERR_BAD_ARG, "%s: bad sizes", who);
+  if (nnz > 0) { REQUIRE_PTR(coo, who); REQUIRE_PTR(tgt_ent, who); }
+  return launch_step_prepare(x, xt, dxt, loss, coo, nnz, label0, L, G, tgt_ptr, tgt_ent, B, D, static_cast<cudaStream_t>(stream));
+}
+
 static int train_step_impl(const StepDump* dump, const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,
                          const uint32_t* tgt_ent, float* dxt, float* loss, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G,
                          int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step,

@@ -174,6 +174,80 @@ __global__ void tgt_fill_kernel(const int32_t* __restrict__ coo, int64_t nnz, in
   }
 }
 
+// ---------------------------------------------------------------- per-step preparation in one launch
+// Block 0 buckets the COO targets entirely in shared memory (count, scan, fill: no global scratch) and clears
+// the loss scalar; every other block transposes one 32x32 tile of x [B,D] -> xt [D,B] and clears the same tile
+// of dxt [D,B].  Replaces one memset, the three bucketing kernels, the transpose and two fills.
+__global__ void __launch_bounds__(256) step_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, float* __restrict__ dxt,
+                                                           float* __restrict__ loss, const int32_t* __restrict__ coo, int64_t nnz,
+                                                           int64_t label0, int64_t L, int G, int NG, int32_t* __restrict__ ptr,
+                                                           uint32_t* __restrict__ ent, int64_t B, int64_t D, int tiles_d) {
+  extern __shared__ int32_t cnt[];          // NG counters, then reused as fill cursors
+  __shared__ int part[256];
+  const int tid = threadIdx.x;
+  if (blockIdx.x == 0) {
+    if (tid == 0 && loss != nullptr) *loss = 0.f;
+    for (int i = tid; i < NG; i += 256) cnt[i] = 0;
+    __syncthreads();
+    for (int64_t i = tid; i < nnz; i += 256) {
+      const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
+      if (c >= 0 && c < L) atomicAdd(&cnt[c / G], 1);
+    }
+    __syncthreads();
+    // exclusive scan of cnt[0..NG): each thread owns a contiguous chunk
+    const int chunk = (NG + 255) / 256, lo = min(NG, tid * chunk), hi = min(NG, lo + chunk);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) sum += cnt[i];
+    part[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0;
+      for (int i = 0; i < 256; ++i) { const int v = part[i]; part[i] = run; run += v; }
+      ptr[NG] = run;
+    }
+    __syncthreads();
+    int run = part[tid];
+    for (int i = lo; i < hi; ++i) { const int v = cnt[i]; ptr[i] = run; cnt[i] = run; run += v; }   // cnt becomes the write cursor
+    __syncthreads();
+    for (int64_t i = tid; i < nnz; i += 256) {
+      const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
+      if (c >= 0 && c < L) {
+        const int64_t g = c / G;
+        const int pos = atomicAdd(&cnt[g], 1);
+        ent[pos] = (static_cast<uint32_t>(coo[2 * i]) << 8) | static_cast<uint32_t>(c - g * G);
+      }
+    }
+    return;
+  }
+  __shared__ uint16_t tile[32][34];
+  const int blk = blockIdx.x - 1;
+  const int64_t d0 = static_cast<int64_t>(blk % tiles_d) * 32, b0 = static_cast<int64_t>(blk / tiles_d) * 32;
+  const int tx = tid & 31, ty = tid >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t b = b0 + j, d = d0 + tx;
+    tile[j][tx] = (b < B && d < D) ? x[b * D + d] : uint16_t(0);
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int64_t d = d0 + j, b = b0 + tx;
+    if (d < D && b < B) { xt[d * B + b] = tile[tx][j]; dxt[d * B + b] = 0.f; }
+  }
+}
+
+int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz, int64_t label0, int64_t L,
+                        int64_t G, int32_t* ptr, uint32_t* ent, int64_t B, int64_t D, cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  const size_t sm = sizeof(int32_t) * static_cast<size_t>(NG);
+  if (sm > 200 * 1024) return fail(HASTE_ERR_TOO_LARGE, "haste_ffi_step_prepare: %lld label groups need more shared memory than one block has; "
+                                   "use haste_transpose_bf16 + haste_targets_bucket", (long long)NG);
+  cudaError_t e = cudaFuncSetAttribute(step_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const int tiles_d = static_cast<int>((D + 31) / 32), tiles_b = static_cast<int>((B + 31) / 32);
+  step_prepare_kernel<<<1 + tiles_d * tiles_b, 256, sm, st>>>((const uint16_t*)x, (uint16_t*)xt, dxt, loss, coo, nnz, label0, L, int(G), int(NG),
+                                                               ptr, ent, B, D, tiles_d);
+  return check_launch("step_prepare_kernel");
+}
+
 __global__ void check_loc_kernel(const int32_t* __restrict__ loc, int64_t n, int D, int* __restrict__ bad) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)

@@ -51,6 +51,8 @@ int launch_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64
                           int32_t* scratch, cudaStream_t st);
 int launch_targets_bucket_noalloc(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G, int32_t* ptr, uint32_t* ent,
                                   cudaStream_t st);
+int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz, int64_t label0, int64_t L,
+                        int64_t G, int32_t* ptr, uint32_t* ent, int64_t B, int64_t D, cudaStream_t st);
 int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st);
 int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int prune_mode,
                   float threshold, int n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,

@@ -115,6 +115,18 @@ def targets_bucket(coo, label0, L, G, tgt_ptr, tgt_ent, scratch):
               "targets_bucket")
 
 
+def step_prepare(x, xt, dxt, loss, coo, label0, L, G, tgt_ptr, tgt_ent):
+    """One launch: xt <- x^T, dxt <- 0, loss <- 0, targets bucketed into (tgt_ptr, tgt_ent)."""
+    _req(x, "x", torch.bfloat16); _req(xt, "xt", torch.bfloat16); _req(dxt, "dxt", torch.float32); _req(coo, "targets", torch.int32)
+    B, D = x.shape
+    nnz = coo.shape[0]
+    if tgt_ent.numel() < nnz:
+        raise RuntimeError("step_prepare: tgt_ent too small")
+    with torch.cuda.device(x.device):
+        check(lib.haste_ffi_step_prepare(_ptr(x), _ptr(xt), _ptr(dxt), _ptr(loss), _ptr(coo), nnz, label0, L, G, _ptr(tgt_ptr),
+                                         _ptr(tgt_ent), B, D, _stream(x)), "ffi_step_prepare")
+
+
 def train_step(loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, mu,
                seed, step, flags):
     _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)

@@ -54,6 +54,7 @@ class FusedFFIShard:
         self.scratch = torch.zeros(self.NG, dtype=torch.int32, device=dev)
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
         self._dxt = None
+        self._xt = None
 
     def _keys(self):
         # reference stream: the optimizer's seed advances by one per step (optim_sr.py:59-62);
@@ -87,8 +88,24 @@ class FusedFFIShard:
         return dxt, (self.loss_buf if want_loss else None)
 
     def step(self, x, targets, want_loss=True):
-        """One step given features [B,D] (bf16, device)."""
-        return self.step_xt(_ffi.transpose_bf16(x), targets, want_loss=want_loss)
+        """One step given features [B,D] (bf16, device): one preparation launch (transpose, clears, target
+        bucketing) and one fused-step launch."""
+        B, D = x.shape
+        if self.NG * 4 > 200 * 1024:                       # too many groups for the single-block bucketing
+            return self.step_xt(_ffi.transpose_bf16(x), targets, want_loss=want_loss)
+        if self._dxt is None or self._dxt.shape != (D, B):
+            self._dxt = torch.empty(D, B, dtype=torch.float32, device=x.device)
+            self._xt = torch.empty(D, B, dtype=torch.bfloat16, device=x.device)
+        if targets.shape[0] > self.tgt_ent.numel():
+            self.tgt_ent = torch.zeros(int(targets.shape[0] * 1.5) + 1, dtype=torch.int32, device=targets.device)
+        _ffi.step_prepare(x, self._xt, self._dxt, self.loss_buf, targets, self.label0, self.L, self.G, self.tgt_ptr, self.tgt_ent)
+        seed, step = self._keys()
+        flags = _ffi.make_flags(sr=self.sr, contract=self.contract, rng=self.rng, zero_dxt=False, loss=want_loss)
+        _ffi.train_step(self.loc, self._xt, self.w, self.bias, self.mom_w, self.mom_b, self.tgt_ptr, self.tgt_ent, self._dxt,
+                        self.loss_buf if want_loss else None, self.G, self.label0, self.loss_kind, self.grad_scale, self.lr,
+                        self.wd, self.mu, seed, step, flags)
+        self.steps += 1
+        return self._dxt, (self.loss_buf if want_loss else None)
 
 
 class ShardedFFILayer:

@@ -98,6 +98,14 @@ int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, voi
 int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_t L, int64_t G,
                          int32_t* tgt_ptr, uint32_t* tgt_ent, int32_t* scratch, haste_stream_t stream);
 
+/* Everything the fused step needs per batch, in one launch: xt = transpose(x [B,D] bf16), dxt cleared, *loss
+ * cleared (loss may be NULL), and the COO targets bucketed as by haste_targets_bucket (counters live in shared
+ * memory, so no scratch argument; at most ~51,000 label groups — HASTE_ERR_TOO_LARGE beyond).
+ * Replaces the transpose of shared_ffi/bindings.py:19 and the per-step zero fills. */
+int haste_ffi_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz,
+                           int64_t label0, int64_t L, int64_t G, int32_t* tgt_ptr, uint32_t* tgt_ent,
+                           int64_t B, int64_t D, haste_stream_t stream);
+
 /* haste_targets_bucket for callers that must not allocate device memory.  (No counterpart in the reference.)
  *
  * Who needs it: a host that gave all device memory to its own arena at start-up and has nothing left to hand

@@ -390,3 +390,28 @@ def test_error_convention(hb):
     with pytest.raises(RuntimeError, match="outside"):
         ffi.check_locations(bad, 64)
     ffi.check_locations(dev["loc"], 64)
+
+
+def test_step_prepare(hb):
+    """The one-launch preparation equals transpose + clears + haste_targets_bucket."""
+    ffi, _ = hb
+    B, D, L, G = 200, 96, 5000, 64
+    inp = fo.make_inputs(B, D, L, 16, G, 12, 1.1, seed=9)
+    x, coo = inp["X"].cuda(), inp["targets"].cuda()
+    for label0, Ls in ((0, L), (1024, 2000)):
+        NG = (Ls + G - 1) // G
+        ptr0 = torch.zeros(NG + 1, dtype=torch.int32, device="cuda")
+        ent0 = torch.zeros(coo.shape[0], dtype=torch.int32, device="cuda")
+        ffi.targets_bucket(coo, label0, Ls, G, ptr0, ent0, torch.zeros(NG, dtype=torch.int32, device="cuda"))
+        ptr1 = torch.full((NG + 1,), -1, dtype=torch.int32, device="cuda")
+        ent1 = torch.full((coo.shape[0],), -1, dtype=torch.int32, device="cuda")
+        xt = torch.empty(D, B, dtype=torch.bfloat16, device="cuda")
+        dxt = torch.full((D, B), 5.0, device="cuda")
+        loss = torch.full((1,), 3.0, device="cuda")
+        ffi.step_prepare(x, xt, dxt, loss, coo, label0, Ls, G, ptr1, ent1)
+        assert torch.equal(xt.cpu(), inp["X"].t().contiguous()) and float(loss) == 0.0 and not dxt.any()
+        p0, p1 = ptr0.cpu().numpy(), ptr1.cpu().numpy()
+        assert np.array_equal(p0, p1)
+        e0, e1 = ent0.cpu().numpy(), ent1.cpu().numpy()
+        for g in np.nonzero(np.diff(p0))[0]:
+            assert sorted(e0[p0[g]:p0[g + 1]]) == sorted(e1[p1[g]:p1[g + 1]])
