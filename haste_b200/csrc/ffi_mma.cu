@@ -14,6 +14,8 @@
 // Bm stored n-major rows (kk contiguous).
 #include "common.cuh"
 #include "launchers.h"
+#include <stdlib.h>
+#include <string.h>
 
 namespace haste {
 
@@ -515,6 +517,10 @@ static int set_smem(K kernel, size_t bytes) {
 
 int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
                    int64_t L, int64_t G, int64_t ldz, cudaStream_t st) {
+  // Shape dispatch: the tcgen05 kernel where its tile shapes apply, the warp-mma kernel otherwise
+  // (HASTE_FWD_IMPL=mma in the environment forces the latter, to compare the two on the same inputs).
+  static const bool force_mma = [] { const char* e = getenv("HASTE_FWD_IMPL"); return e != nullptr && strcmp(e, "mma") == 0; }();
+  if (!force_mma && forward_sm100_supported(z, B, F, G, ldz)) return launch_forward_sm100(loc, xt, w, bias, z, B, D, F, L, G, ldz, st);
   const int64_t NG = (L + G - 1) / G;
   dim3 grid(static_cast<unsigned>(NG), static_cast<unsigned>((B + BT - 1) / BT));
   const size_t sm = fwd_smem(int(G), int(F));

@@ -109,3 +109,20 @@ def test_sm100_step_repeatable_weights(hb):
     r2 = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, 1.0, "packed")
     assert torch.equal(r1[0], r2[0]) and torch.equal(r1[1], r2[1])
     assert torch.allclose(r1[2], r2[2], rtol=1e-5, atol=1e-5 * float(r1[2].abs().max()))
+
+
+@pytest.mark.parametrize("shape", SHAPES + [(512, 768, 670091 // 16)])
+def test_sm100_forward(hb, shape):
+    """tcgen05 forward (G=128, F=64) against the oracle, including the zero padding columns and the no-bias case."""
+    ffi, _ = hb
+    B, D, L = shape
+    inp = fo.make_inputs(B, D, L, F, G, 2, 1.1, seed=L, x_kind="normal", bias_zero=False)
+    dev = {k: v.cuda() for k, v in inp.items()}
+    xt = dev["X"].t().contiguous()
+    for bias in (dev["bias"], None):
+        z = ffi.forward(dev["loc"], xt, dev["W"], bias, G)
+        want = fo.forward(inp["loc"], inp["X"], inp["W"], inp["bias"] if bias is not None else None, G, round_bf16=False)
+        _close(z, want, 1e-2, 1e-3 * max(1.0, float(want.abs().max())), "forward")
+        ldz = (L + 7) // 8 * 8
+        if ldz > L:
+            assert (torch.as_strided(z, (B, ldz), (ldz, 1))[:, L:] == 0).all()
