@@ -485,6 +485,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
                 gq[i] = fmaf(0.5f, th, 0.5f) * gs;
                 if (WITH_LOSS) tile_loss += fmaxf(z[i], 0.f) - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
               }
+            } else if (LOSS == HASTE_LOSS_BCE && !ragged) {
+              // with positives: dLoss/dz = sigmoid(z) - y, loss = max(z,0) - y z - ln(0.5 + 0.5 |tanh(z/2)|)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float y = static_cast<float>((ym8 >> i) & 1u);
+                float th;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z[i]));
+                gq[i] = (fmaf(0.5f, th, 0.5f) - y) * gs;
+                if (WITH_LOSS) tile_loss += fmaxf(z[i], 0.f) - y * z[i] - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
+              }
             } else if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
               // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
 #pragma unroll
