@@ -56,7 +56,8 @@ static_assert(NBAR <= 32, "barrier space");
 // TMEM columns
 // Z double-buffered (2 x 128), dXg double-buffered (2 x 64), dW single (64 + 16)
 constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
-constexpr int NTHREADS = 768;                    // 4 control warps + 16 epilogue-A warps + 4 epilogue-B warps
+constexpr int N_EB = 8;                          // epilogue-B warps: 4 TMEM lane quarters x 2 slot halves
+constexpr int NTHREADS = (4 + 16 + N_EB) * 32;   // 4 control warps + 16 epilogue-A warps + epilogue-B warps
 constexpr int N_EA = 16;                         // epilogue-A warps: 4 TMEM lane quarters x 4 column quarters
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
@@ -122,8 +123,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
       mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EA);
       mbar_init(bar(B_YFULL + i), N_EA);  mbar_init(bar(B_YEMPTY + i), 2);   // both backward issuers commit
-      mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), 4);
-      mbar_init(bar(B_MEMPTY + i), N_EA + 4);   // every epilogue warp is done with the group's index/bias rows and W tile
+      mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), N_EB);
+      mbar_init(bar(B_MEMPTY + i), N_EA + N_EB);   // every epilogue warp is done with the group's index/bias rows and W tile
     }
     mbar_init(bar(B_DWFULL), 1);
     mbar_init(bar(B_DWEMPTY), N_EA);
@@ -561,12 +562,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 12, WAIT_LIMIT);
         tc_fence_after();
         if (bt == 0) TR(3, 1000 + it);
-        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + (ds ? F : 0);
-        uint32_t r0[32], r1[32];
+        const int kh = (warp - (4 + N_EA)) >> 2;      // which half of the 64 slots this warp scatters
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + (ds ? F : 0) + kh * 32;
+        uint32_t r0[32];
         tmem_ld32(ta, r0);
-        tmem_ld32(ta + 32, r1);
         tmem_ld_wait();
-        tc_fence_before();                         // the whole dXg tile is in registers: hand the buffer back at once
+        tc_fence_before();                         // this warp's half of the dXg tile is in registers: hand it back at once
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_DXEMPTY + ds));
         // dXg[b,k] of this thread's batch row goes to dxt[loc[k], b]: for a fixed k the warp's 32 lanes hit 32
@@ -575,19 +576,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           float* dbase = a.dxt + b0 + row;
 #pragma unroll
           for (int k4 = 0; k4 < 32; k4 += 4) {
-            const int4 lc = loc4[k4 >> 2];
+            const int4 lc = loc4[kh * 8 + (k4 >> 2)];
             atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r0[k4 + 0]));
             atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r0[k4 + 1]));
             atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r0[k4 + 2]));
             atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r0[k4 + 3]));
-          }
-#pragma unroll
-          for (int k4 = 0; k4 < 32; k4 += 4) {
-            const int4 lc = loc4[8 + (k4 >> 2)];
-            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r1[k4 + 0]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r1[k4 + 1]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r1[k4 + 2]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r1[k4 + 3]));
           }
         }
         if (bt == 0) TR(3, 2000 + it);
