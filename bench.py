@@ -349,6 +349,7 @@ def run_aux(args):
         ("ffi_forward (unfused, writes Z)", lambda: hffi.forward(loc, xt, W, bias, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_features (unfused, reads dY)", lambda: hffi.backward_features(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_weights (unfused, reads dY, writes dW)", lambda: hffi.backward_weights(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
+        ("ffi_backward (both gradients, one pass over dY incl. row padding)", lambda: hffi.backward_both(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 2 * L * F + 4 * NG * F),
         ("ffi_bww_sr_sgd (backward-weights + SGD/SR, no dW)", lambda: hffi.bww_sr_sgd(xt, loc, dy, w2, None, None, None, G, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 2 * B * L + 4 * L * F + 4 * NG * F),
         ("sgd_sr_update packed stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 6 * L * F),
         ("sgd_sr_update reference stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="reference")), 6 * L * F),

@@ -24,6 +24,8 @@ SIGNATURES = {
     "haste_ffi_forward": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, P],
     "haste_ffi_backward_features": [P, P, P, P, I64, I64, I64, I64, I64, I64, U32, P],
     "haste_ffi_backward_weights": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, P],
+    "haste_ffi_backward": [P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, U32, P],
+    "haste_pad_rows_bf16": [P, I64, P, I64, I64, I64, P],
     "haste_ffi_bww_sr_sgd": [P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F32, F32, F32, U64, U32, U32, P],
     "haste_targets_bucket": [P, I64, I64, I64, I64, P, P, P, P],
     "haste_ffi_step_prepare": [P, P, P, P, P, I64, I64, I64, I64, P, P, I64, I64, P],

@@ -11,12 +11,6 @@ namespace haste {
 
 static thread_local char g_err[512] = "no error";
 
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-}
 int fail(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -98,6 +92,30 @@ int haste_ffi_backward_weights(const void* xt, const int32_t* loc, const void* d
   if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
   if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
   return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_backward(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
+                       int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, uint32_t flags, haste_stream_t stream) {
+  const char* who = "haste_ffi_backward";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(dy, who); REQUIRE_PTR(dxt, who); REQUIRE_PTR(dw, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(dxt, who); REQUIRE_ALIGNED(dw, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (flags & HASTE_F_ZERO_DXT) {
+    cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
+    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
+  }
+  if (backward_sm100_supported(dy, dw, B, F, G, ldy)) return launch_backward_sm100(xt, w, loc, dy, dxt, dw, dbias, B, D, F, L, G, ldy, st);
+  if (int rc = launch_bwd_features(w, loc, dy, dxt, B, D, F, L, G, ldy, st)) return rc;
+  return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, st);
+}
+
+int haste_pad_rows_bf16(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols, haste_stream_t stream) {
+  const char* who = "haste_pad_rows_bf16";
+  REQUIRE_PTR(src, who); REQUIRE_PTR(dst, who); REQUIRE_ALIGNED(dst, who);
+  if (rows < 1 || cols < 1 || ld_src < cols || ld_dst < cols || (ld_dst % 8) != 0) return fail(HASTE_ERR_BAD_ARG, "%s: bad sizes", who);
+  return launch_pad_rows(src, ld_src, dst, ld_dst, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
 int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, void* w, void* bias, float* mom_w, float* mom_b, int64_t B,

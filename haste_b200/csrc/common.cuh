@@ -12,7 +12,6 @@
 namespace haste {
 
 // ---------------------------------------------------------------- host error plumbing
-void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 int validate_shape(const char* who, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G);
@@ -50,8 +49,6 @@ __device__ __forceinline__ uint32_t rand16_reference(uint64_t seed, int64_t flat
                                 static_cast<uint32_t>(seed >> 32));
   return r.x & 0xFFFFu;
 }
-// out-of-line copy for code-size-sensitive callers
-__device__ __noinline__ static uint32_t rand16_reference_call(uint64_t seed, int64_t flat) { return rand16_reference(seed, flat); }
 __device__ __forceinline__ uint4 rand_packed8(uint64_t seed, uint32_t step, int64_t row, int col8) {
   return philox4x32_10(static_cast<uint32_t>(row), static_cast<uint32_t>(col8), 0u, 0u,
                        static_cast<uint32_t>(seed), step);

@@ -248,6 +248,30 @@ int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const 
   return check_launch("step_prepare_kernel");
 }
 
+// ---------------------------------------------------------------- row padding: [rows, cols] (stride ld_src) -> [rows, ld_dst], zeros past cols
+__global__ void __launch_bounds__(256) pad_rows_kernel(const uint16_t* __restrict__ src, int64_t ld_src, uint16_t* __restrict__ dst,
+                                                       int64_t ld_dst, int64_t rows, int64_t cols) {
+  const int64_t chunks = ld_dst >> 3;                      // ld_dst % 8 == 0, dst 16-byte aligned
+  const int64_t n = rows * chunks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t r = i / chunks, c = (i - r * chunks) << 3;
+    const uint16_t* p = src + r * ld_src + c;
+    uint16_t e[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) e[k] = (c + k < cols) ? p[k] : uint16_t(0);
+    uint4 v;
+    v.x = e[0] | (uint32_t(e[1]) << 16); v.y = e[2] | (uint32_t(e[3]) << 16);
+    v.z = e[4] | (uint32_t(e[5]) << 16); v.w = e[6] | (uint32_t(e[7]) << 16);
+    *reinterpret_cast<uint4*>(dst + r * ld_dst + c) = v;
+  }
+}
+
+int launch_pad_rows(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols, cudaStream_t st) {
+  pad_rows_kernel<<<grid_for(rows * (ld_dst >> 3), 256), 256, 0, st>>>((const uint16_t*)src, ld_src, (uint16_t*)dst, ld_dst, rows, cols);
+  return check_launch("pad_rows_kernel");
+}
+
 __global__ void check_loc_kernel(const int32_t* __restrict__ loc, int64_t n, int D, int* __restrict__ bad) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)

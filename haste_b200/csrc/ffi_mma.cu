@@ -102,11 +102,6 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* s, int lds, int rows, i
   }
 }
 
-struct GroupCtx {
-  const int32_t* loc_row;   // loc + g*F
-  int64_t l0;               // first label of the group (shard-local)
-  int rows_real;            // min(G, L - l0)
-};
 
 __device__ __forceinline__ void load_loc(int* locs, const int32_t* loc_row, int F, int D, int tid) {
   for (int k = tid; k < F; k += NT) {

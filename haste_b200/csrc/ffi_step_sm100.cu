@@ -25,6 +25,9 @@
 
 namespace haste {
 namespace s100 {
+// out-of-line Philox for the reference random stream: that path is slow anyway and must not bloat the epilogue code
+__device__ __noinline__ static uint32_t rand16_reference_call(uint64_t seed, int64_t flat) { return rand16_reference(seed, flat); }
+
 using namespace sm100;
 
 constexpr int G = 128, F = 64, BT = 128;

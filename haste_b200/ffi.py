@@ -94,6 +94,28 @@ def backward_weights(xt, w, loc, dy, G, want_dbias=False):
     return (dw, db) if want_dbias else dw
 
 
+def backward_both(xt, w, loc, dy, G, want_dbias=True):
+    """(dxt fp32 [D,B], dw bf16 [L,F], dbias bf16 [L] or None) from one pass over dy where the shape allows."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    dy, ldy = _rows(dy, L)
+    dev = xt.device
+    with torch.cuda.device(dev):
+        if G == 128 and F == 64 and B % 8 == 0 and (ldy % 8 != 0 or dy.data_ptr() % 16 != 0):
+            # give the rows 16-byte alignment (one extra pass over dy, still cheaper than reading it twice unaligned)
+            ldp = (L + 7) // 8 * 8
+            padded = torch.empty(B, ldp, dtype=torch.bfloat16, device=dev)
+            check(lib.haste_pad_rows_bf16(_ptr(dy), ldy, _ptr(padded), ldp, B, L, _stream(xt)), "pad_rows_bf16")
+            dy, ldy = padded, ldp
+        dxt = torch.empty(D, B, dtype=torch.float32, device=dev)
+        dw = torch.empty(L, F, dtype=torch.bfloat16, device=dev)
+        db = torch.empty(L, dtype=torch.bfloat16, device=dev) if want_dbias else None
+        check(lib.haste_ffi_backward(_ptr(xt), _ptr(w), _ptr(loc), _ptr(dy), _ptr(dxt), _ptr(dw), _ptr(db), B, D, F, L, G, ldy,
+                                     _lib.F_ZERO_DXT, _stream(xt)), "ffi_backward")
+    return dxt, dw, db
+
+
 def bww_sr_sgd(xt, loc, dy, w, bias, mom_w, mom_b, G, label0, lr, wd, mu, seed, step, flags):
     _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
     D, B = xt.shape

@@ -31,6 +31,14 @@ class GroupFFIMulFunction(torch.autograd.Function):
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         need_b = ctx.use_bias and ctx.needs_input_grad[3]
         input_gradient = weight_gradient = bias_gradient = None
+        if need_x and need_w:
+            # both gradients from one pass over grad_output
+            dxt, weight_gradient, bias_gradient = _ffi.backward_both(features_t, weights, group_locations, grad_output, gsize,
+                                                                     want_dbias=bool(need_b))
+            input_gradient = _ffi.dxt_to_dx_sr(dxt, 123)
+            if ctx.in_dtype != torch.bfloat16:
+                input_gradient = input_gradient.to(ctx.in_dtype)
+            return input_gradient, weight_gradient, None, bias_gradient, None
         if need_x:
             dxt = _ffi.backward_features(features_t, weights, group_locations, grad_output, gsize)
             # bindings.py:44-50 of the reference: transpose, then stochastic rounding with the fixed seed 123

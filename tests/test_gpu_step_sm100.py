@@ -126,3 +126,26 @@ def test_sm100_forward(hb, shape):
         ldz = (L + 7) // 8 * 8
         if ldz > L:
             assert (torch.as_strided(z, (B, ldz), (ldz, 1))[:, L:] == 0).all()
+
+
+@pytest.mark.parametrize("shape", SHAPES + [(512, 768, 670091 // 16)])
+def test_sm100_backward_both(hb, shape):
+    """One-pass tcgen05 backward (G=128, F=64): dxt, dw and dbias against the oracle, for gradient rows that need
+    padding (L % 8 != 0) and rows that are already aligned."""
+    ffi, _ = hb
+    B, D, L = shape
+    inp = fo.make_inputs(B, D, L, F, G, 2, 1.1, seed=L + 1, x_kind="normal", bias_zero=False)
+    dev = {k: v.cuda() for k, v in inp.items()}
+    xt = dev["X"].t().contiguous()
+    gen = torch.Generator().manual_seed(3)
+    dY = (torch.randn(B, L, generator=gen) * 0.5).to(torch.bfloat16)
+    ldp = (L + 7) // 8 * 8
+    aligned = torch.zeros(B, ldp, dtype=torch.bfloat16, device="cuda")
+    aligned[:, :L] = dY.cuda()
+    want_x = fo.backward_features(inp["loc"], inp["W"], dY, G, D)
+    want_w = fo.backward_weights(inp["loc"], inp["X"], dY, G, L, round_bf16=False)
+    for dy_dev in (dY.cuda(), aligned[:, :L]):
+        dxt, dw, db = ffi.backward_both(xt, dev["W"], dev["loc"], dy_dev, G)
+        _close(dxt, want_x, 1e-2, 1e-3 * max(1.0, float(want_x.abs().max())), "dXt")
+        _close(dw, want_w, 1e-2, 1e-3 * max(1.0, float(want_w.abs().max())), "dW")
+        _close(db, dY.float().sum(0), 1e-2, 2e-2, "dbias")
