@@ -39,7 +39,7 @@ int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
                       const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
                       cudaStream_t st, const StepDump* dump) {
   static const bool force_mma = [] { const char* e = getenv("HASTE_STEP_IMPL"); return e != nullptr && strcmp(e, "mma") == 0; }();
-  if (!force_mma && train_step_sm100_supported(B, F, G, u))
+  if (!force_mma && train_step_sm100_supported(B, D, F, G, u))
     return launch_train_step_sm100(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st, dump);
   if (dump != nullptr) return fail(HASTE_ERR_UNSUPPORTED, "debug outputs exist only in the tcgen05 fused step (G=128, F=64, B%%8==0, no momentum)");
   return launch_train_step_mma(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);

@@ -60,8 +60,11 @@ static_assert(NBAR <= 32, "barrier space");
 // Z double-buffered (2 x 128), dXg double-buffered (2 x 64), dW single (64 + 16)
 constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
 constexpr int N_EB = 8;                          // epilogue-B warps: 4 TMEM lane quarters x 2 slot halves
-constexpr int NTHREADS = (4 + 16 + N_EB) * 32;   // 4 control warps + 16 epilogue-A warps + epilogue-B warps
-constexpr int N_EA = 16;                         // epilogue-A warps: 4 TMEM lane quarters x 4 column quarters
+constexpr int N_EA = 8;                          // epilogue-A warps: 4 TMEM lane quarters x (N_EA/4) column ranges
+constexpr int NTHREADS = (4 + N_EA + N_EB) * 32; // 4 control warps + epilogue-A warps + epilogue-B warps
+constexpr int EA_COLS = G * 4 / N_EA;            // label columns of a tile handled by one epilogue-A warp (32 or 64)
+constexpr int EA_SLOTS = F * 4 / N_EA;           // slots of a finished group updated by one epilogue-A warp (16 or 32)
+static_assert(N_EA == 8 || N_EA == 16, "epilogue A is written for 8 or 16 warps");
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
 #ifdef HASTE_TRACE
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(sm);
   float* bias_s = reinterpret_cast<float*>(sm + OFF_BIAS);
-  int* loc_s = reinterpret_cast<int*>(sm + OFF_LOC);
+  uint32_t* loc_s = reinterpret_cast<uint32_t*>(sm + OFF_LOC);   // per slot: element offset loc * B of its dxt row
   uint32_t* ybits = reinterpret_cast<uint32_t*>(sm + OFF_YB);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 8);
@@ -181,8 +184,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT, 100);
         mbar_wait(bar(B_MEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 1, WAIT_LIMIT, 100);
         __syncwarp();
-        loc_s[ws * F + lane] = loc_lo;
-        loc_s[ws * F + lane + 32] = loc_hi;
+        loc_s[ws * F + lane] = static_cast<uint32_t>(loc_lo) * static_cast<uint32_t>(a.B);        // D * B < 2^32 is a launch condition
+        loc_s[ws * F + lane + 32] = static_cast<uint32_t>(loc_hi) * static_cast<uint32_t>(a.B);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int c = lane * 4 + i;
@@ -316,13 +319,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     }
   } else if (warp >= 4 && warp < 4 + N_EA) {
     // ================================================================ epilogue A: Z -> dY
-    const int ea = warp - 4, q = ea & 3, cq = ea >> 2;   // TMEM lane quarter, column quarter (32 labels each)
+    const int ea = warp - 4, q = ea & 3, h = ea >> 2;    // TMEM lane quarter, column range (EA_COLS labels each)
     const int row = q * 32 + lane;               // batch row inside the tile == TMEM lane
-    const int et = tid - 128;                    // 0..511
+    const int et = tid - 128;                    // 0..N_EA*32-1
     float loss_acc = 0.f;
     int it = 0;
-    // Weight / bias update of one finished group from its dW accumulator: warp (q, cq) owns label rows
-    // q*32..q*32+31 and slots cq*16..cq*16+15 (two Philox calls in the packed stream).  Runs one batch tile
+    // Weight / bias update of one finished group from its dW accumulator: warp (q, h) owns label rows
+    // q*32..q*32+31 and slots h*EA_SLOTS.. in pieces of 16 (two Philox calls each in the packed stream).  Runs one batch tile
     // behind the group's own tiles so the accumulator is certainly complete and the tensor core is not held up.
     auto update_group = [&](int gu) {
       const int gg = blockIdx.x + gu * gridDim.x;
@@ -332,14 +335,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
       tc_fence_after();
       const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
+#pragma unroll 1
+      for (int cq = h * (EA_SLOTS / 16); cq < (h + 1) * (EA_SLOTS / 16); ++cq) {
       uint32_t r[16], rb[8];
       __syncwarp();
       tmem_ld16(tdw + cq * 16, r);
       if (HAS_BIAS && cq == 0) tmem_ld8(tdw + F, rb);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+      if (cq == (h + 1) * (EA_SLOTS / 16) - 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+      }
       if (row < rows_real_u && !*abort_flag) {
         const int64_t l = l0 + row, gl = u.label0 + l;
         const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
@@ -389,6 +396,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
         }
       }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / index row / bias row
     };
@@ -402,19 +410,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       for (int t = 0; t < T; ++t, ++it) {
         const int zs = it & 1;
         const int64_t b0 = tile_b0(t);
-        uint32_t ym32 = 0u;
+        uint64_t ym = 0ull;                              // target bits of this thread's row, EA_COLS label columns
         if (has_t && t_end - t_beg <= 8) {
           // Few targets in this group (the common case): each thread picks the bits of its own row and 32 label
           // columns straight from the entry list — no shared bitmap, no barrier between the epilogue warps.
           const uint32_t rowkey = static_cast<uint32_t>(b0 + row);
           for (int i = t_beg; i < t_end; ++i) {
             const uint32_t e = __ldg(a.tgt_ent + i);
-            const uint32_t c = (e & 0xFFu) - static_cast<uint32_t>(cq * 32);
-            if ((e >> 8) == rowkey && c < 32u) ym32 |= 1u << c;
+            const uint32_t c = (e & 0xFFu) - static_cast<uint32_t>(h * EA_COLS);
+            if ((e >> 8) == rowkey && c < static_cast<uint32_t>(EA_COLS)) ym |= 1ull << c;
           }
         } else if (has_t) {
           uint32_t* yb = ybits + (it & 1) * BT * 4;
-          yb[et] = 0u;
+          for (int i = et; i < BT * 4; i += N_EA * 32) yb[i] = 0u;
           named_bar_sync(1, N_EA * 32);
           for (int i = t_beg + et; i < t_end; i += N_EA * 32) {
             const uint32_t e = __ldg(a.tgt_ent + i);
@@ -423,7 +431,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             if (rb >= 0 && rb < BT && c < G) atomicOr(&yb[rb * 4 + (c >> 5)], 1u << (c & 31));
           }
           named_bar_sync(1, N_EA * 32);
-          ym32 = yb[row * 4 + cq];
+          if (EA_COLS == 32) ym = yb[row * 4 + h];
+          else ym = static_cast<uint64_t>(yb[row * 4 + h * 2]) | (static_cast<uint64_t>(yb[row * 4 + h * 2 + 1]) << 32);
         }
         const bool row_valid = b0 + row < a.B;
         const float gs = row_valid ? a.grad_scale : 0.f;
@@ -432,23 +441,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         mbar_wait(bar(B_YEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
         tc_fence_after();
         if (ea == 0 && lane == 0) TR(2, 2000 + it);
-        const int col0 = cq * 32;                                  // first label column of this warp
-        uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + (cq >> 1) * YBLK + row * 128;
+        const int col0 = h * EA_COLS;                              // first label column of this warp
+        uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + (col0 >> 6) * YBLK + row * 128;
         const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + col0;
         const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + col0);
         const float gs2 = 2.f * gs;
         const float inv_gs2_sq = row_valid ? 1.f / (gs2 * gs2) : 0.f;
-        const bool ragged = col0 + 32 > rows_real;     // only the last group of the layer can be ragged
+        const bool ragged = col0 + EA_COLS > rows_real;     // only the last group of the layer can be ragged
         float tile_loss = 0.f, fast_loss = 0.f;
         // two 16-column chunks in a real loop (small code: four roles share each scheduler's instruction cache);
         // with four epilogue-A warps per scheduler the TMEM load latency is covered by the other warps
 #pragma unroll 1
-        for (int c16 = 0; c16 < 32; c16 += 16) {
+        for (int c16 = 0; c16 < EA_COLS; c16 += 16) {
           uint32_t r[16];
           __syncwarp();
           tmem_ld16(ta + c16, r);
           tmem_ld_wait();
-          const uint32_t ym16 = (ym32 >> c16) & 0xFFFFu;
+          const uint32_t ym16 = static_cast<uint32_t>(ym >> c16) & 0xFFFFu;
 #pragma unroll
           for (int e8 = 0; e8 < 16; e8 += 8) {
             float z[8];
@@ -558,7 +567,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int ws = gi & 1;
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 11, WAIT_LIMIT);   // loc_s of this group is in place
-      const int4* loc4 = reinterpret_cast<const int4*>(loc_s + ws * F);
+      const uint4* loc4 = reinterpret_cast<const uint4*>(loc_s + ws * F);
       for (int t = 0; t < T; ++t, ++it) {
         const int64_t b0 = tile_b0(t);
         const int ds = it & 1;
@@ -579,11 +588,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           float* dbase = a.dxt + b0 + row;
 #pragma unroll
           for (int k4 = 0; k4 < 32; k4 += 4) {
-            const int4 lc = loc4[kh * 8 + (k4 >> 2)];
-            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r0[k4 + 0]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r0[k4 + 1]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r0[k4 + 2]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r0[k4 + 3]));
+            const uint4 lc = loc4[kh * 8 + (k4 >> 2)];      // 32-bit row offsets: one widening add per address
+            atomicAdd(dbase + lc.x, __uint_as_float(r0[k4 + 0]));
+            atomicAdd(dbase + lc.y, __uint_as_float(r0[k4 + 1]));
+            atomicAdd(dbase + lc.z, __uint_as_float(r0[k4 + 2]));
+            atomicAdd(dbase + lc.w, __uint_as_float(r0[k4 + 3]));
           }
         }
         if (bt == 0) TR(3, 2000 + it);
@@ -614,8 +623,8 @@ static int ensure_err_flag() {
 
 }  // namespace s100
 
-bool train_step_sm100_supported(int64_t B, int64_t F, int64_t G, const UpdateArgs& u) {
-  return G == s100::G && F == s100::F && (B % 8) == 0 && u.mom_w == nullptr && u.mom_b == nullptr;
+bool train_step_sm100_supported(int64_t B, int64_t D, int64_t F, int64_t G, const UpdateArgs& u) {
+  return G == s100::G && F == s100::F && (B % 8) == 0 && D * B < (int64_t(1) << 32) && u.mom_w == nullptr && u.mom_b == nullptr;
 }
 
 int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
