@@ -63,17 +63,16 @@ constexpr int N_EB = 8;                          // epilogue-B warps: 4 TMEM lan
 constexpr int N_EA = 8;                          // epilogue-A warps: 4 TMEM lane quarters x (N_EA/4) column ranges
 constexpr int NTHREADS = (4 + N_EA + N_EB) * 32; // 4 control warps + epilogue-A warps + epilogue-B warps
 constexpr int EA_COLS = G * 4 / N_EA;            // label columns of a tile handled by one epilogue-A warp (32 or 64)
-constexpr int EA_SLOTS = F * 4 / N_EA;           // slots of a finished group updated by one epilogue-A warp (16 or 32)
+constexpr int EB_SLOTS = F * 4 / N_EB;           // slots scattered and updated by one epilogue-B warp
 static_assert(N_EA == 8 || N_EA == 16, "epilogue A is written for 8 or 16 warps");
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
 #ifdef HASTE_TRACE
 // development build only: per-role event timeline of CTA 0
-__device__ long long g_trace[4][2048][2];
-__device__ int g_trace_n[4];
+__device__ unsigned long long g_trace[6][2048];     // (clock << 16) | event, zero = unused
 #define TR(role, ev)                                                        \
   do {                                                                      \
-    if (blockIdx.x == 0 && tr_n < 2048) { g_trace[role][tr_n][0] = (ev); g_trace[role][tr_n][1] = clock64(); ++tr_n; g_trace_n[role] = tr_n; } \
+    if (blockIdx.x == 0 && tr_n < 2048) { g_trace[role][tr_n++] = (static_cast<unsigned long long>(clock64()) << 16) | static_cast<unsigned>(ev); } \
   } while (0)
 #else
 #define TR(role, ev) do {} while (0)
@@ -133,7 +132,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       mbar_init(bar(B_MEMPTY + i), N_EA + N_EB);   // every epilogue warp is done with the group's index/bias rows and W tile
     }
     mbar_init(bar(B_DWFULL), 1);
-    mbar_init(bar(B_DWEMPTY), N_EA);
+    mbar_init(bar(B_DWEMPTY), N_EB);
     mbar_fence_init();
     *abort_flag = 0;
   }
@@ -197,8 +196,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           const int idx = i * 32 + lane, r = idx >> 3, c = idx & 7;
           cp_async16(wb + r * 128 + ((c ^ (r & 7)) << 4), u.w + (l0 + r) * F + c * 8, r < rows_real);
         }
-        if (lane == 0) TR(0, 100 + gi);
+        if (lane == 0) TR(p * 4, 100 + gi);
         land(bar(B_WFULL + ws));
+        if (lane == 0) TR(p * 4, 500 + gi);
       }
       ++item;
       // ---- X items: one per batch tile
@@ -219,8 +219,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           const __nv_bfloat16* src = a.xt + static_cast<int64_t>(lk) * a.B + b0 + j * 8;
           cp_async16(xb + ((dcol + k * 128) ^ ((k & 7) << 4)), valid ? src : a.xt, valid);
         }
-        if (lane == 0) TR(0, 1000 + it);
+        if (lane == 0) TR(p * 4, 1000 + it);
         land(bar(B_XFULL + xs));
+        if (lane == 0) TR(p * 4, 5000 + it);
       }
     }
   } else if (warp == 1 || warp == 3) {
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             // Y(t) complete implies forward(t) complete, so the tile's X slot is loaded as well
             mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 14, WAIT_LIMIT);
             tc_fence_after();
+            TR(5, 1000 + j);
             const uint32_t ym = ym_lo + (ys ? (YSTAGE >> 4) : 0u), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
             // dW[l,k] += sum over batch chunks of Y[b-chunk, l]^T * X[k, b-chunk]
             umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
@@ -311,6 +313,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
               umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
             tc_commit(bar(B_YEMPTY + ys));
             tc_commit(bar(B_XEMPTY + xs));
+            TR(5, 2000 + j);
             if (++xs == NXS) xs = 0;
           }
           tc_commit(bar(B_DWFULL));
@@ -324,82 +327,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     const int et = tid - 128;                    // 0..N_EA*32-1
     float loss_acc = 0.f;
     int it = 0;
-    // Weight / bias update of one finished group from its dW accumulator: warp (q, h) owns label rows
-    // q*32..q*32+31 and slots h*EA_SLOTS.. in pieces of 16 (two Philox calls each in the packed stream).  Runs one batch tile
-    // behind the group's own tiles so the accumulator is certainly complete and the tensor core is not held up.
-    auto update_group = [&](int gu) {
-      const int gg = blockIdx.x + gu * gridDim.x;
-      const int wsu = gu & 1;
-      const int64_t l0 = static_cast<int64_t>(gg) * G;
-      const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
-      mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
-      tc_fence_after();
-      const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
-#pragma unroll 1
-      for (int cq = h * (EA_SLOTS / 16); cq < (h + 1) * (EA_SLOTS / 16); ++cq) {
-      uint32_t r[16], rb[8];
-      __syncwarp();
-      tmem_ld16(tdw + cq * 16, r);
-      if (HAS_BIAS && cq == 0) tmem_ld8(tdw + F, rb);
-      tmem_ld_wait();
-      if (cq == (h + 1) * (EA_SLOTS / 16) - 1) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
-      }
-      if (row < rows_real_u && !*abort_flag) {
-        const int64_t l = l0 + row, gl = u.label0 + l;
-        const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
-        __nv_bfloat16* wrow = u.w + l * F;
-        const uint8_t* wsm = sm + OFF_W + wsu * WSTAGE + row * 128;   // the group's W tile still holds the old weights
-        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
-        if (sr) {
-          if (packed) {
-            const uint4 rp0 = rand_packed8(u.seed, u.step, gl, cq * 2), rp1 = rand_packed8(u.seed, u.step, gl, cq * 2 + 1);
-            rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
-            rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
-          } else {
-#pragma unroll
-            for (int x = 0; x < 16; x += 2)
-              rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + cq * 16 + x) | (rand16_reference_call(u.seed, gl * F + cq * 16 + x + 1) << 16);
-          }
-        }
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int c8 = cq * 2 + hf;
-          const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
-          const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
-          uint32_t ob[4];
-#pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
-            // the gradient is first rounded to bf16, as the unfused kernel would store it
-            const uint32_t gp = pack_bf16x2(a0, a1);
-            if (DEBUG) { if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp; }
-            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
-            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
-            float n0, n1;
-            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            const uint32_t rr = rnd[hf * 4 + p];
-            const uint32_t o0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
-            const uint32_t o1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
-            ob[p] = (o0 & 0xFFFFu) | (o1 << 16);
-          }
-          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-        }
-        if (HAS_BIAS && cq == 0) {
-          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
-          if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
-          uint32_t r16 = 0;
-          if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
-          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
-        }
-      }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / index row / bias row
-    };
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
@@ -549,10 +476,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_YFULL + zs));
         if (ea == 0 && lane == 0) TR(2, 3000 + it);
-        if (t == 0 && gi > 0) update_group(gi - 1);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));    // this warp no longer needs the group's bias row
     }
-    if (n_my_groups > 0) update_group(n_my_groups - 1);
     if (WITH_LOSS) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) loss_acc += __shfl_xor_sync(0xffffffffu, loss_acc, o);
@@ -563,6 +490,89 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     const int q = warp & 3;
     const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
     const int bt = tid - (4 + N_EA) * 32;        // 0..127
+    const int kh = (warp - (4 + N_EA)) >> 2;     // which part of the 64 slots this warp scatters and updates
+    // Weight / bias update of one finished group from its dW accumulator: warp (q, kh) owns label rows
+    // q*32..q*32+31 and slots kh*EB_SLOTS.. in pieces of 16 (two Philox calls each in the packed stream).  These
+    // warps have time to spare between scatters, and the group's accumulator is handed back to the tensor core
+    // as soon as it has been read.
+    auto update_group = [&](int gu) {
+      const int gg = blockIdx.x + gu * gridDim.x;
+      const int wsu = gu & 1;
+      const int64_t l0 = static_cast<int64_t>(gg) * G;
+      const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
+      if (bt == 0) TR(3, 4000 + gu);
+      mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
+      if (bt == 0) TR(3, 4500 + gu);
+      tc_fence_after();
+      const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
+#pragma unroll 1
+      for (int cq = kh * (EB_SLOTS / 16); cq < (kh + 1) * (EB_SLOTS / 16); ++cq) {
+      uint32_t r[16], rb[8];
+      __syncwarp();
+      tmem_ld16(tdw + cq * 16, r);
+      if (HAS_BIAS && cq == 0) tmem_ld8(tdw + F, rb);
+      tmem_ld_wait();
+      if (cq == (kh + 1) * (EB_SLOTS / 16) - 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+      }
+      if (row < rows_real_u && !*abort_flag) {
+        const int64_t l = l0 + row, gl = u.label0 + l;
+        const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
+        __nv_bfloat16* wrow = u.w + l * F;
+        const uint8_t* wsm = sm + OFF_W + wsu * WSTAGE + row * 128;   // the group's W tile still holds the old weights
+        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
+        if (sr) {
+          if (packed) {
+            const uint4 rp0 = rand_packed8(u.seed, u.step, gl, cq * 2), rp1 = rand_packed8(u.seed, u.step, gl, cq * 2 + 1);
+            rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
+            rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
+          } else {
+#pragma unroll
+            for (int x = 0; x < 16; x += 2)
+              rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + cq * 16 + x) | (rand16_reference_call(u.seed, gl * F + cq * 16 + x + 1) << 16);
+          }
+        }
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int c8 = cq * 2 + hf;
+          const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
+          const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
+          uint32_t ob[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
+            // the gradient is first rounded to bf16, as the unfused kernel would store it
+            const uint32_t gp = pack_bf16x2(a0, a1);
+            if (DEBUG) { if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp; }
+            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
+            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
+            float n0, n1;
+            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            const uint32_t rr = rnd[hf * 4 + p];
+            const uint32_t o0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
+            const uint32_t o1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
+            ob[p] = (o0 & 0xFFFFu) | (o1 << 16);
+          }
+          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+        if (HAS_BIAS && cq == 0) {
+          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
+          if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
+          uint32_t r16 = 0;
+          if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
+          // the old bias comes from the group's bias row in shared memory (the fp32 image of the bf16 value: exact)
+          const uint16_t b_old = __bfloat16_as_ushort(__float2bfloat16_rn(bias_s[wsu * G + row]));
+          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(b_old, gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
+        }
+      }
+      }
+      __syncwarp();
+      if (bt == 0) TR(3, 6000 + gu);
+      if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / index row / bias row
+    };
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int ws = gi & 1;
@@ -574,7 +584,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 12, WAIT_LIMIT);
         tc_fence_after();
         if (bt == 0) TR(3, 1000 + it);
-        const int kh = (warp - (4 + N_EA)) >> 2;      // which half of the 64 slots this warp scatters
         const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + (ds ? F : 0) + kh * 32;
         uint32_t r0[32];
         tmem_ld32(ta, r0);
@@ -597,8 +606,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         }
         if (bt == 0) TR(3, 2000 + it);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));
+      update_group(gi);                          // ends with this warp's arrival on the group's MEMPTY barrier
     }
   }
 
@@ -676,10 +684,11 @@ int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* t
 #ifdef HASTE_TRACE
 extern "C" int haste_dbg_trace_dump(long long* out, int* counts) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, haste::s100::g_trace, sizeof(long long) * 4 * 2048 * 2);
-  cudaMemcpyFromSymbol(counts, haste::s100::g_trace_n, sizeof(int) * 4);
-  int z[4] = {0, 0, 0, 0};
-  cudaMemcpyToSymbol(haste::s100::g_trace_n, z, sizeof(z));
+  (void)counts;
+  cudaMemcpyFromSymbol(out, haste::s100::g_trace, sizeof(long long) * 6 * 2048);
+  void* p = nullptr;
+  cudaGetSymbolAddress(&p, haste::s100::g_trace);
+  cudaMemset(p, 0, sizeof(long long) * 6 * 2048);
   return 0;
 }
 #endif
