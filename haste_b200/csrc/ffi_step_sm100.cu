@@ -60,16 +60,18 @@ static_assert(NBAR <= 32, "barrier space");
 // Z double-buffered (2 x 128), dXg double-buffered (2 x 64), dW single (64 + 16)
 constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
 constexpr int N_EB = 8;                          // epilogue-B warps: 4 TMEM lane quarters x 2 slot halves
-constexpr int N_EA = 8;                          // epilogue-A warps: 4 TMEM lane quarters x (N_EA/4) column ranges
+constexpr int N_EA_SET = 8;                      // epilogue-A warps working on one tile: 4 TMEM lane quarters x 2 column halves
+constexpr int N_SETS = 2;                        // sets of epilogue-A warps; set s takes the tiles whose Z stage is s
+constexpr int N_EA = N_EA_SET * N_SETS;
 constexpr int NTHREADS = (4 + N_EA + N_EB) * 32; // 4 control warps + epilogue-A warps + epilogue-B warps
-constexpr int EA_COLS = G * 4 / N_EA;            // label columns of a tile handled by one epilogue-A warp (32 or 64)
+constexpr int EA_COLS = G * 4 / N_EA_SET;        // label columns of a tile handled by one epilogue-A warp (32 or 64)
 constexpr int EB_SLOTS = F * 4 / N_EB;           // slots scattered and updated by one epilogue-B warp
-static_assert(N_EA == 8 || N_EA == 16, "epilogue A is written for 8 or 16 warps");
+static_assert((N_EA_SET == 8 || N_EA_SET == 16) && (N_SETS == 1 || N_SETS == 2), "epilogue A: 8 or 16 warps per tile, one or two sets");
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
 #ifdef HASTE_TRACE
 // development build only: per-role event timeline of CTA 0
-__device__ unsigned long long g_trace[6][2048];     // (clock << 16) | event, zero = unused
+__device__ unsigned long long g_trace[7][2048];     // (clock << 16) | event, zero = unused
 #define TR(role, ev)                                                        \
   do {                                                                      \
     if (blockIdx.x == 0 && tr_n < 2048) { g_trace[role][tr_n++] = (static_cast<unsigned long long>(clock64()) << 16) | static_cast<unsigned>(ev); } \
@@ -101,6 +103,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Two fp32 -> one bf16x2 word with max(0, .) applied to both halves (one conversion instruction).
+__device__ __forceinline__ uint32_t pack_bf16x2_relu(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// v rounded to bf16 (nearest even), returned as fp32: converting (v, 0) to a bf16x2 word puts bf16(v) in the
+// upper half over a zero lower half, which is the fp32 image of the rounded value — no unpacking needed.
+__device__ __forceinline__ float round_bf16_as_f32(float v) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(v), "f"(0.f));
+  return __uint_as_float(d);
+}
+
 template <int LOSS, bool WITH_LOSS, bool HAS_BIAS, bool DEBUG>
 __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u) {
   extern __shared__ uint8_t smem_raw[];
@@ -126,8 +142,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     for (int i = 0; i < NXS; ++i) { mbar_init(bar(B_XFULL + i), 1); mbar_init(bar(B_XEMPTY + i), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
-      mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EA);
-      mbar_init(bar(B_YFULL + i), N_EA);  mbar_init(bar(B_YEMPTY + i), 2);   // both backward issuers commit
+      mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EA_SET);
+      mbar_init(bar(B_YFULL + i), N_EA_SET);  mbar_init(bar(B_YEMPTY + i), 2);   // both backward issuers commit
       mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), N_EB);
       mbar_init(bar(B_MEMPTY + i), N_EA + N_EB);   // every epilogue warp is done with the group's index/bias rows and W tile
     }
@@ -322,10 +338,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     }
   } else if (warp >= 4 && warp < 4 + N_EA) {
     // ================================================================ epilogue A: Z -> dY
-    const int ea = warp - 4, q = ea & 3, h = ea >> 2;    // TMEM lane quarter, column range (EA_COLS labels each)
+    // With two sets, a set works on every other tile: the waits, fences and TMEM latencies of one set's tile are
+    // covered by the other set's arithmetic.
+    const int ea = warp - 4, set = ea / N_EA_SET, es = ea % N_EA_SET;
+    const int q = es & 3, h = es >> 2;           // TMEM lane quarter, column range (EA_COLS labels each)
     const int row = q * 32 + lane;               // batch row inside the tile == TMEM lane
-    const int et = tid - 128;                    // 0..N_EA*32-1
+    const int et = tid - 128 - set * N_EA_SET * 32;   // thread index inside the set
     float loss_acc = 0.f;
+    const float inv_4gs2_sq = 0.0625f / (a.grad_scale * a.grad_scale);   // undoes the (4 s)^2 carried by the fast loss sum
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
@@ -335,6 +355,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       const bool has_t = t_end > t_beg;
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 8, WAIT_LIMIT);   // bias_s of this group is in place
       for (int t = 0; t < T; ++t, ++it) {
+        if (N_SETS > 1 && (it & 1) != set) continue;     // the other set's tile
         const int zs = it & 1;
         const int64_t b0 = tile_b0(t);
         uint64_t ym = 0ull;                              // target bits of this thread's row, EA_COLS label columns
@@ -349,31 +370,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           }
         } else if (has_t) {
           uint32_t* yb = ybits + (it & 1) * BT * 4;
-          for (int i = et; i < BT * 4; i += N_EA * 32) yb[i] = 0u;
-          named_bar_sync(1, N_EA * 32);
-          for (int i = t_beg + et; i < t_end; i += N_EA * 32) {
+          for (int i = et; i < BT * 4; i += N_EA_SET * 32) yb[i] = 0u;
+          named_bar_sync(1 + set, N_EA_SET * 32);
+          for (int i = t_beg + et; i < t_end; i += N_EA_SET * 32) {
             const uint32_t e = __ldg(a.tgt_ent + i);
             const int64_t rb = static_cast<int64_t>(e >> 8) - b0;
             const int c = e & 0xFF;
             if (rb >= 0 && rb < BT && c < G) atomicOr(&yb[rb * 4 + (c >> 5)], 1u << (c & 31));
           }
-          named_bar_sync(1, N_EA * 32);
+          named_bar_sync(1 + set, N_EA_SET * 32);
           if (EA_COLS == 32) ym = yb[row * 4 + h];
           else ym = static_cast<uint64_t>(yb[row * 4 + h * 2]) | (static_cast<uint64_t>(yb[row * 4 + h * 2 + 1]) << 32);
         }
         const bool row_valid = b0 + row < a.B;
         const float gs = row_valid ? a.grad_scale : 0.f;
         mbar_wait(bar(B_ZFULL + zs), (it >> 1) & 1, abort_flag, a.err, 9, WAIT_LIMIT);
-        if (ea == 0 && lane == 0) TR(2, 1000 + it);
+        if (es == 0 && lane == 0) TR(2 + 4 * set, 1000 + it);
         mbar_wait(bar(B_YEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
         tc_fence_after();
-        if (ea == 0 && lane == 0) TR(2, 2000 + it);
+        if (es == 0 && lane == 0) TR(2 + 4 * set, 2000 + it);
         const int col0 = h * EA_COLS;                              // first label column of this warp
         uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + (col0 >> 6) * YBLK + row * 128;
         const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + col0;
         const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + col0);
         const float gs2 = 2.f * gs;
-        const float inv_gs2_sq = row_valid ? 1.f / (gs2 * gs2) : 0.f;
+        const float inv_gs2_sq = row_valid ? inv_4gs2_sq : 0.f;
         const bool ragged = col0 + EA_COLS > rows_real;     // only the last group of the layer can be ragged
         float tile_loss = 0.f, fast_loss = 0.f;
         // two 16-column chunks in a real loop (small code: four roles share each scheduler's instruction cache);
@@ -382,8 +403,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         for (int c16 = 0; c16 < EA_COLS; c16 += 16) {
           uint32_t r[16];
           __syncwarp();
+          if (es == 0 && lane == 0) TR(2 + 4 * set, 7000 + c16);
           tmem_ld16(ta + c16, r);
           tmem_ld_wait();
+          if (es == 0 && lane == 0) TR(2 + 4 * set, 8000 + c16);
           const uint32_t ym16 = static_cast<uint32_t>(ym >> c16) & 0xFFFFu;
 #pragma unroll
           for (int e8 = 0; e8 < 16; e8 += 8) {
@@ -395,24 +418,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
               z[4] = __uint_as_float(r[e8 + 4]) + bb.x; z[5] = __uint_as_float(r[e8 + 5]) + bb.y;
               z[6] = __uint_as_float(r[e8 + 6]) + bb.z; z[7] = __uint_as_float(r[e8 + 7]) + bb.w;
             }
-            uint32_t zp[4];                            // logits rounded to bf16, as the unfused forward stores them
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              zp[p] = pack_bf16x2(z[2 * p], z[2 * p + 1]);
-              z[2 * p] = __uint_as_float(zp[p] << 16);
-              z[2 * p + 1] = __uint_as_float(zp[p] & 0xFFFF0000u);
-            }
+            for (int i = 0; i < 8; ++i) z[i] = round_bf16_as_f32(z[i]);   // logits rounded to bf16, as the unfused forward stores them
             const uint32_t ym8 = (ym16 >> e8) & 0xFFu;
             float gq[8];
+            bool relu = false;
             if (LOSS == HASTE_LOSS_SQHINGE && !ragged && ym16 == 0u) {
               // no positive among these labels (the common case): dLoss/dz = 2 s max(0, 1 + z) with s = grad_scale,
               // evaluated as max(0, fma(2s, z, 2s)); 1 + z is exact in fp32 for a bf16 z (down to |z| ~ 2^-16), so
-              // this is the same single rounding as (1 + z) * 2s.  The loss term max(0,1+z)^2 is accumulated as
-              // g^2 and rescaled by 1/(2s)^2 once per tile.
+              // this is the same single rounding as (1 + z) * 2s.  The max is left to the bf16 conversion below.
+              // The loss term max(0,1+z)^2 is accumulated as (x + |x|)^2 = (2 max(0,x))^2 and rescaled by
+              // 1/(4s)^2 once per tile: adds and multiply-adds only, which run beside the conversions.
+              relu = true;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                gq[i] = fmaxf(fmaf(gs2, z[i], gs2), 0.f);
-                if (WITH_LOSS) fast_loss = fmaf(gq[i], gq[i], fast_loss);
+                gq[i] = fmaf(gs2, z[i], gs2);
+                if (WITH_LOSS) { const float m2 = gq[i] + fabsf(gq[i]); fast_loss = fmaf(m2, m2, fast_loss); }
               }
             } else if (LOSS == HASTE_LOSS_BCE && !ragged && ym16 == 0u) {
               // no positive among these labels: dLoss/dz = sigmoid(z) = 0.5 + 0.5 tanh(z/2) (one MUFU op);
@@ -459,23 +480,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
                 uint16_t* zd = reinterpret_cast<uint16_t*>(a.z_dump) + (b0 + row) * a.ldz + static_cast<int64_t>(g) * G + col0 + c16 + e8;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  if (col0 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>((i & 1) ? (zp[i >> 1] >> 16) : (zp[i >> 1] & 0xFFFFu));
+                  if (col0 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>(__float_as_uint(z[i]) >> 16);
               }
             }
             const int chunk = ((col0 & 63) + c16 + e8) >> 3;       // 16-byte chunk inside the 128-byte row of this block
             *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) =
-                make_uint4(pack_bf16x2(gq[0], gq[1]), pack_bf16x2(gq[2], gq[3]), pack_bf16x2(gq[4], gq[5]), pack_bf16x2(gq[6], gq[7]));
+                relu ? make_uint4(pack_bf16x2_relu(gq[0], gq[1]), pack_bf16x2_relu(gq[2], gq[3]), pack_bf16x2_relu(gq[4], gq[5]), pack_bf16x2_relu(gq[6], gq[7]))
+                     : make_uint4(pack_bf16x2(gq[0], gq[1]), pack_bf16x2(gq[2], gq[3]), pack_bf16x2(gq[4], gq[5]), pack_bf16x2(gq[6], gq[7]));
           }
         }
         tc_fence_before();                             // this warp's half of the Z stage has been read
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
         if (WITH_LOSS && row_valid) loss_acc += tile_loss + fast_loss * inv_gs2_sq;
-        if (ea == 0 && lane == 0) TR(2, 2700 + it);
+        if (es == 0 && lane == 0) TR(2 + 4 * set, 2700 + it);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_YFULL + zs));
-        if (ea == 0 && lane == 0) TR(2, 3000 + it);
+        if (es == 0 && lane == 0) TR(2 + 4 * set, 3000 + it);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));    // this warp no longer needs the group's bias row
@@ -685,10 +707,10 @@ int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* t
 extern "C" int haste_dbg_trace_dump(long long* out, int* counts) {
   cudaDeviceSynchronize();
   (void)counts;
-  cudaMemcpyFromSymbol(out, haste::s100::g_trace, sizeof(long long) * 6 * 2048);
+  cudaMemcpyFromSymbol(out, haste::s100::g_trace, sizeof(long long) * 7 * 2048);
   void* p = nullptr;
   cudaGetSymbolAddress(&p, haste::s100::g_trace);
-  cudaMemset(p, 0, sizeof(long long) * 6 * 2048);
+  cudaMemset(p, 0, sizeof(long long) * 7 * 2048);
   return 0;
 }
 #endif
