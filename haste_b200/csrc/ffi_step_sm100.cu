@@ -27,12 +27,16 @@ namespace haste {
 namespace s100 {
 // out-of-line Philox for the reference random stream: that path is slow anyway and must not bloat the epilogue code
 __device__ __noinline__ static uint32_t rand16_reference_call(uint64_t seed, int64_t flat) { return rand16_reference(seed, flat); }
+// likewise one shared copy of the packed-stream generator and of the bias draw for the update warps
+__device__ __noinline__ static uint4 rand_packed8_call(uint64_t seed, uint32_t step, int64_t row, int col8) { return rand_packed8(seed, step, row, col8); }
+__device__ __noinline__ static uint32_t rand16_call(uint32_t flags, uint64_t seed, uint32_t step, int64_t row) { return rand16(flags, seed, step, row, 0, 1); }
 
 using namespace sm100;
 
 constexpr int G = 128, F = 64, BT = 128;
 constexpr int FR = F + 16;                    // rows of an X block: F gathered rows, one row of ones, 15 zero rows
 constexpr int NXS = 6;                        // X ring stages
+constexpr int NYS = 2;                        // dY ring stages
 constexpr int XBLK = FR * 128;                // one 64-batch block of an X stage (bytes)
 constexpr int XSTAGE = 2 * XBLK;
 constexpr int WSTAGE = G * 128;
@@ -41,7 +45,7 @@ constexpr int YSTAGE = 2 * YBLK;
 constexpr int OFF_X = 0;
 constexpr int OFF_W = OFF_X + NXS * XSTAGE;
 constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
-constexpr int OFF_BIAS = OFF_Y + 2 * YSTAGE;         // float [2][G]
+constexpr int OFF_BIAS = OFF_Y + NYS * YSTAGE;         // float [2][G]
 constexpr int OFF_LOC = OFF_BIAS + 2 * G * 4;        // int   [2][F]
 constexpr int OFF_YB = OFF_LOC + 2 * F * 4;          // u32   [2][BT][4]  target bits
 constexpr int OFF_BAR = OFF_YB + 2 * BT * 4 * 4;     // mbarriers
@@ -51,7 +55,7 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
 // barrier indices
 constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_WFULL = 2 * NXS, B_WEMPTY = B_WFULL + 2, B_ZFULL = B_WEMPTY + 2,
-              B_ZEMPTY = B_ZFULL + 2, B_YFULL = B_ZEMPTY + 2, B_YEMPTY = B_YFULL + 2, B_DXFULL = B_YEMPTY + 2,
+              B_ZEMPTY = B_ZFULL + 2, B_YFULL = B_ZEMPTY + 2, B_YEMPTY = B_YFULL + NYS, B_DXFULL = B_YEMPTY + NYS,
               B_DXEMPTY = B_DXFULL + 2, B_DWFULL = B_DXEMPTY + 2, B_DWEMPTY = B_DWFULL + 1, B_MEMPTY = B_DWEMPTY + 1,
               NBAR = B_MEMPTY + 2;
 static_assert(NBAR <= 32, "barrier space");
@@ -61,11 +65,14 @@ static_assert(NBAR <= 32, "barrier space");
 constexpr uint32_t TM_Z = 0, TM_DX = 256, TM_DW = 384, TM_COLS = 512;
 constexpr int N_EB = 8;                          // epilogue-B warps: 4 TMEM lane quarters x 2 slot halves
 constexpr int N_EA_SET = 8;                      // epilogue-A warps working on one tile: 4 TMEM lane quarters x 2 column halves
-constexpr int N_SETS = 2;                        // sets of epilogue-A warps; set s takes the tiles whose Z stage is s
+constexpr int N_SETS = 1;                        // sets of epilogue-A warps; set s takes the tiles whose Z stage is s
 constexpr int N_EA = N_EA_SET * N_SETS;
-constexpr int NTHREADS = (4 + N_EA + N_EB) * 32; // 4 control warps + epilogue-A warps + epilogue-B warps
+constexpr int BX_LAG = N_SETS;                   // backward-features runs this many tiles behind the forward product
+constexpr int N_UP = 8;                          // update warps: 4 TMEM lane quarters x 2 slot halves
+constexpr int NTHREADS = (4 + N_EA + N_EB + N_UP) * 32;   // 4 control warps + epilogue-A + epilogue-B + update warps
+static_assert(NTHREADS <= 1024, "thread budget");
 constexpr int EA_COLS = G * 4 / N_EA_SET;        // label columns of a tile handled by one epilogue-A warp (32 or 64)
-constexpr int EB_SLOTS = F * 4 / N_EB;           // slots scattered and updated by one epilogue-B warp
+constexpr int UP_SLOTS = F * 4 / N_UP;           // slots updated by one update warp
 static_assert((N_EA_SET == 8 || N_EA_SET == 16) && (N_SETS == 1 || N_SETS == 2), "epilogue A: 8 or 16 warps per tile, one or two sets");
 constexpr long long WAIT_LIMIT = 4000000000ll;   // clock cycles (~2 s) before a wait gives up
 
@@ -143,12 +150,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
       mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EA_SET);
-      mbar_init(bar(B_YFULL + i), N_EA_SET);  mbar_init(bar(B_YEMPTY + i), 2);   // both backward issuers commit
       mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), N_EB);
-      mbar_init(bar(B_MEMPTY + i), N_EA + N_EB);   // every epilogue warp is done with the group's index/bias rows and W tile
+      mbar_init(bar(B_MEMPTY + i), N_EA + N_EB + N_UP);   // every epilogue warp is done with the group's index/bias rows and W tile
     }
+    for (int i = 0; i < NYS; ++i) { mbar_init(bar(B_YFULL + i), N_EA_SET); mbar_init(bar(B_YEMPTY + i), 2); }   // both backward issuers commit
     mbar_init(bar(B_DWFULL), 1);
-    mbar_init(bar(B_DWEMPTY), N_EB);
+    mbar_init(bar(B_DWEMPTY), N_UP);
     mbar_fence_init();
     *abort_flag = 0;
   }
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     // Feeding the tensor pipe from a single thread costs more cycles per tcgen05.mma than the small (N = 64..128)
     // products take to execute, so the work is split: warp 1 issues forward + backward-features, warp 3 issues
     // backward-weights.  Both hang off the same mbarriers; the pipe executes in arrival order.
-    if (lane == 0) {
+    {
       constexpr uint32_t ID_FWD = make_idesc(128, G, 1, 0);
       constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
       constexpr uint32_t ID_BWW = make_idesc(128, N_DW, 1, 0);
@@ -265,74 +272,94 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         const uint32_t wm_lo = static_cast<uint32_t>(D_WM), wm_hi = static_cast<uint32_t>(D_WM >> 32);
         const uint32_t ya_lo = static_cast<uint32_t>(D_YA), ya_hi = static_cast<uint32_t>(D_YA >> 32);
         const uint32_t id_fwd = ID_FWD, id_bwx = ID_BWX;
+        // Order of issue: forward(it) first, then backward-features of tile it - BX_LAG.  Both become possible at
+        // the same moment (epilogue A finished a tile); the forward product goes first because an epilogue-A
+        // set is waiting for it, while nothing waits for the backward product's dY stage (three stages).
         int it = 0, xs = 0, xph = 0;
-        auto backward_x = [&](int j, int ws) {
-          const int ys = j & 1;
-          mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 2, WAIT_LIMIT);
-          mbar_wait(bar(B_DXEMPTY + ys), ((j >> 1) & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
+        int j = 0, jy = 0, jyph = 0, j_t = 0, j_g = 0;     // next backward-features tile: dY stage and phase, position in its group
+        auto backward_x = [&]() {
+          const int ds = j & 1, ws = j_g & 1;
+          mbar_wait(bar(B_YFULL + jy), jyph, abort_flag, a.err, 2, WAIT_LIMIT);
+          mbar_wait(bar(B_DXEMPTY + ds), ((j >> 1) & 1) ^ 1, abort_flag, a.err, 3, WAIT_LIMIT);
           tc_fence_after();
-          TR(1, 2000 + j);
-          const uint32_t ya = ya_lo + (ys ? (YSTAGE >> 4) : 0u), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
-          const uint32_t tdx = tmem + TM_DX + (ys ? F : 0);
+          if (lane == 0) TR(1, 2000 + j);
+          const uint32_t ya = ya_lo + static_cast<uint32_t>(jy) * (YSTAGE >> 4), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
+          const uint32_t tdx = tmem + TM_DX + (ds ? F : 0);
           // dXg[b,k] = sum over label chunks of Y[b, l-chunk] * W[l-chunk, k]
-          umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
+          const bool last_of_group = j_t + 1 == T;
+          if (elect_one()) {
+            umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
 #pragma unroll
-          for (int ks = 1; ks < G / 16; ++ks)
-            umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
-          tc_commit(bar(B_DXFULL + ys));
-          tc_commit(bar(B_YEMPTY + ys));
-          TR(1, 3000 + j);
+            for (int ks = 1; ks < G / 16; ++ks)
+              umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
+            tc_commit(bar(B_DXFULL + ds));
+            tc_commit(bar(B_YEMPTY + jy));
+            if (last_of_group) tc_commit(bar(B_WEMPTY + ws));   // every product that reads this group's W tile has been issued
+          }
+          __syncwarp();
+          if (lane == 0) TR(1, 3000 + j);
+          if (++jy == NYS) { jy = 0; jyph ^= 1; }
+          ++j;
+          if (++j_t == T) { j_t = 0; ++j_g; }
         };
         for (int gi = 0; gi < n_my_groups; ++gi) {
           const int ws = gi & 1;
+          // the W stage of this group was last used by group gi - 2: its products must all be issued before the
+          // stage can be refilled (matters only when a group has fewer tiles than the lag)
+          while (j < it && j_g + 2 <= gi) backward_x();
           mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 5, WAIT_LIMIT);
           for (int t = 0; t < T; ++t, ++it) {
             const int zs = it & 1;
             mbar_wait(bar(B_XFULL + xs), xph, abort_flag, a.err, 6, WAIT_LIMIT);
             mbar_wait(bar(B_ZEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 7, WAIT_LIMIT);
             tc_fence_after();
-            TR(1, 1000 + it);
+            if (lane == 0) TR(1, 1000 + it);
             const uint32_t xa = xa_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4), wb = wb_lo + (ws ? (WSTAGE >> 4) : 0u);
             const uint32_t tz = tmem + TM_Z + (zs ? G : 0);
             // Z[b,l] = sum over slot chunks of X[k-chunk, b]^T * W[l, k-chunk]
-            umma_bf16_lohi<false>(tz, xa, xa_hi, wb, wb_hi, id_fwd);
+            if (elect_one()) {
+              umma_bf16_lohi<false>(tz, xa, xa_hi, wb, wb_hi, id_fwd);
 #pragma unroll
-            for (int ks = 1; ks < F / 16; ++ks)
-              umma_bf16_lohi<true>(tz, xa + ((ks * 2048) >> 4), xa_hi, wb + ((ks * 32) >> 4), wb_hi, id_fwd);
-            tc_commit(bar(B_ZFULL + zs));
+              for (int ks = 1; ks < F / 16; ++ks)
+                umma_bf16_lohi<true>(tz, xa + ((ks * 2048) >> 4), xa_hi, wb + ((ks * 32) >> 4), wb_hi, id_fwd);
+              tc_commit(bar(B_ZFULL + zs));
+            }
+            __syncwarp();
             if (++xs == NXS) { xs = 0; xph ^= 1; }
-            if (t > 0) backward_x(it - 1, ws);
+            if (it >= BX_LAG) backward_x();
           }
-          backward_x(it - 1, ws);
-          tc_commit(bar(B_WEMPTY + ws));          // every product that reads this group's W tile has been issued
         }
+        while (j < it) backward_x();
       } else {
         // ---------------- backward-weights
         const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
         const uint32_t ym_lo = static_cast<uint32_t>(D_YM), ym_hi = static_cast<uint32_t>(D_YM >> 32);
         const uint32_t id_bww = ID_BWW;
-        int j = 0, xs = 0;
+        int j = 0, xs = 0, jy = 0, jyph = 0;
         for (int gi = 0; gi < n_my_groups; ++gi) {
           const uint32_t tdw = tmem + TM_DW;
           mbar_wait(bar(B_DWEMPTY), (gi & 1) ^ 1, abort_flag, a.err, 4, WAIT_LIMIT);
           for (int t = 0; t < T; ++t, ++j) {
-            const int ys = j & 1;
             // Y(t) complete implies forward(t) complete, so the tile's X slot is loaded as well
-            mbar_wait(bar(B_YFULL + ys), (j >> 1) & 1, abort_flag, a.err, 14, WAIT_LIMIT);
+            mbar_wait(bar(B_YFULL + jy), jyph, abort_flag, a.err, 14, WAIT_LIMIT);
             tc_fence_after();
-            TR(5, 1000 + j);
-            const uint32_t ym = ym_lo + (ys ? (YSTAGE >> 4) : 0u), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
+            if (lane == 0) TR(5, 1000 + j);
+            const uint32_t ym = ym_lo + static_cast<uint32_t>(jy) * (YSTAGE >> 4), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
             // dW[l,k] += sum over batch chunks of Y[b-chunk, l]^T * X[k, b-chunk]
-            umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
+            if (elect_one()) {
+              umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
 #pragma unroll
-            for (int ks = 1; ks < BT / 16; ++ks)
-              umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
-            tc_commit(bar(B_YEMPTY + ys));
-            tc_commit(bar(B_XEMPTY + xs));
-            TR(5, 2000 + j);
+              for (int ks = 1; ks < BT / 16; ++ks)
+                umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
+              tc_commit(bar(B_YEMPTY + jy));
+              tc_commit(bar(B_XEMPTY + xs));
+              if (t + 1 == T) tc_commit(bar(B_DWFULL));
+            }
+            __syncwarp();
+            if (++jy == NYS) { jy = 0; jyph ^= 1; }
+            if (lane == 0) TR(5, 2000 + j);
             if (++xs == NXS) xs = 0;
           }
-          tc_commit(bar(B_DWFULL));
         }
       }
     }
@@ -346,7 +373,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     const int et = tid - 128 - set * N_EA_SET * 32;   // thread index inside the set
     float loss_acc = 0.f;
     const float inv_4gs2_sq = 0.0625f / (a.grad_scale * a.grad_scale);   // undoes the (4 s)^2 carried by the fast loss sum
-    int it = 0;
+    int it = 0, ys = 0, yph = 0;                 // global tile counter, its dY stage and phase
+    auto next_tile = [&]() { ++it; if (++ys == NYS) { ys = 0; yph ^= 1; } };
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
@@ -354,7 +382,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       const int t_beg = __ldg(a.tgt_ptr + g), t_end = __ldg(a.tgt_ptr + g + 1);
       const bool has_t = t_end > t_beg;
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 8, WAIT_LIMIT);   // bias_s of this group is in place
-      for (int t = 0; t < T; ++t, ++it) {
+      for (int t = 0; t < T; ++t, next_tile()) {
         if (N_SETS > 1 && (it & 1) != set) continue;     // the other set's tile
         const int zs = it & 1;
         const int64_t b0 = tile_b0(t);
@@ -386,19 +414,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         const float gs = row_valid ? a.grad_scale : 0.f;
         mbar_wait(bar(B_ZFULL + zs), (it >> 1) & 1, abort_flag, a.err, 9, WAIT_LIMIT);
         if (es == 0 && lane == 0) TR(2 + 4 * set, 1000 + it);
-        mbar_wait(bar(B_YEMPTY + zs), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
+        mbar_wait(bar(B_YEMPTY + ys), yph ^ 1, abort_flag, a.err, 10, WAIT_LIMIT);
         tc_fence_after();
         if (es == 0 && lane == 0) TR(2 + 4 * set, 2000 + it);
         const int col0 = h * EA_COLS;                              // first label column of this warp
-        uint8_t* ytile = sm + OFF_Y + zs * YSTAGE + (col0 >> 6) * YBLK + row * 128;
+        uint8_t* ytile = sm + OFF_Y + ys * YSTAGE + (col0 >> 6) * YBLK + row * 128;
         const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_Z + zs * G + col0;
         const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + col0);
         const float gs2 = 2.f * gs;
         const float inv_gs2_sq = row_valid ? inv_4gs2_sq : 0.f;
         const bool ragged = col0 + EA_COLS > rows_real;     // only the last group of the layer can be ragged
         float tile_loss = 0.f, fast_loss = 0.f;
-        // two 16-column chunks in a real loop (small code: four roles share each scheduler's instruction cache);
-        // with four epilogue-A warps per scheduler the TMEM load latency is covered by the other warps
+        // 16 label columns per iteration.  Nearly every chunk has no positive label in the warp's 32 rows and no
+        // ragged edge: one warp vote per chunk sends those down a branch with no per-element tests (which would cost
+        // about a quarter of the epilogue's instructions); the rest take the general branch with target bits and a
+        // column-valid mask.
 #pragma unroll 1
         for (int c16 = 0; c16 < EA_COLS; c16 += 16) {
           uint32_t r[16];
@@ -408,85 +438,85 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           tmem_ld_wait();
           if (es == 0 && lane == 0) TR(2 + 4 * set, 8000 + c16);
           const uint32_t ym16 = static_cast<uint32_t>(ym >> c16) & 0xFFFFu;
+          const bool general = DEBUG || ragged || __any_sync(0xffffffffu, ym16 != 0u);
+          if (!general) {
 #pragma unroll
-          for (int e8 = 0; e8 < 16; e8 += 8) {
-            float z[8];
-            {
+            for (int e8 = 0; e8 < 16; e8 += 8) {
               const float4 ba = bs4[(c16 + e8) >> 2], bb = bs4[((c16 + e8) >> 2) + 1];
+              float z[8];
               z[0] = __uint_as_float(r[e8 + 0]) + ba.x; z[1] = __uint_as_float(r[e8 + 1]) + ba.y;
               z[2] = __uint_as_float(r[e8 + 2]) + ba.z; z[3] = __uint_as_float(r[e8 + 3]) + ba.w;
               z[4] = __uint_as_float(r[e8 + 4]) + bb.x; z[5] = __uint_as_float(r[e8 + 5]) + bb.y;
               z[6] = __uint_as_float(r[e8 + 6]) + bb.z; z[7] = __uint_as_float(r[e8 + 7]) + bb.w;
+              uint4 pk;
+              if (LOSS == HASTE_LOSS_SQHINGE) {
+                // dLoss/dz = 2 s max(0, 1 + z) with s = grad_scale, evaluated as max(0, fma(2s, z, 2s)); 1 + z is
+                // exact in fp32 for a bf16 z (down to |z| ~ 2^-16), so this is the same single rounding as
+                // (1 + z) * 2s.  The max is left to the bf16 conversion.  The loss term max(0,1+z)^2 is accumulated
+                // as (x + |x|)^2 = (2 max(0,x))^2 and rescaled by 1/(4s)^2 once per tile.
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  x[i] = fmaf(gs2, round_bf16_as_f32(z[i]), gs2);   // logits are rounded to bf16 first, as the unfused forward stores them
+                  if (WITH_LOSS) { const float m2 = x[i] + fabsf(x[i]); fast_loss = fmaf(m2, m2, fast_loss); }
+                }
+                pk = make_uint4(pack_bf16x2_relu(x[0], x[1]), pack_bf16x2_relu(x[2], x[3]), pack_bf16x2_relu(x[4], x[5]), pack_bf16x2_relu(x[6], x[7]));
+              } else {
+                // dLoss/dz = sigmoid(z) = 0.5 + 0.5 tanh(z/2) (one MUFU op); loss term softplus(z) =
+                // max(z,0) - ln(0.5 + 0.5 |tanh(z/2)|), whose logarithm argument stays in [0.5, 1]
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float zr = round_bf16_as_f32(z[i]);
+                  float th;
+                  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * zr));
+                  x[i] = fmaf(0.5f, th, 0.5f) * gs;
+                  if (WITH_LOSS) tile_loss += fmaxf(zr, 0.f) - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
+                }
+                pk = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+              }
+              const int chunk = ((col0 & 63) + c16 + e8) >> 3;     // 16-byte chunk inside the 128-byte row of this block
+              *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) = pk;
             }
+          } else {
+            const int nvalid = rows_real - (col0 + c16);           // columns of this chunk that are real labels
 #pragma unroll
-            for (int i = 0; i < 8; ++i) z[i] = round_bf16_as_f32(z[i]);   // logits rounded to bf16, as the unfused forward stores them
-            const uint32_t ym8 = (ym16 >> e8) & 0xFFu;
-            float gq[8];
-            bool relu = false;
-            if (LOSS == HASTE_LOSS_SQHINGE && !ragged && ym16 == 0u) {
-              // no positive among these labels (the common case): dLoss/dz = 2 s max(0, 1 + z) with s = grad_scale,
-              // evaluated as max(0, fma(2s, z, 2s)); 1 + z is exact in fp32 for a bf16 z (down to |z| ~ 2^-16), so
-              // this is the same single rounding as (1 + z) * 2s.  The max is left to the bf16 conversion below.
-              // The loss term max(0,1+z)^2 is accumulated as (x + |x|)^2 = (2 max(0,x))^2 and rescaled by
-              // 1/(4s)^2 once per tile: adds and multiply-adds only, which run beside the conversions.
-              relu = true;
+            for (int e8 = 0; e8 < 16; e8 += 8) {
+              const float4 ba = bs4[(c16 + e8) >> 2], bb = bs4[((c16 + e8) >> 2) + 1];
+              const float bias8[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
+              float x[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                gq[i] = fmaf(gs2, z[i], gs2);
-                if (WITH_LOSS) { const float m2 = gq[i] + fabsf(gq[i]); fast_loss = fmaf(m2, m2, fast_loss); }
-              }
-            } else if (LOSS == HASTE_LOSS_BCE && !ragged && ym16 == 0u) {
-              // no positive among these labels: dLoss/dz = sigmoid(z) = 0.5 + 0.5 tanh(z/2) (one MUFU op);
-              // loss term softplus(z) = max(z,0) - ln(max(sigmoid, 1 - sigmoid)) = max(z,0) - ln(0.5 + 0.5 |tanh(z/2)|),
-              // whose logarithm argument stays in [0.5, 1] (no cancellation for large |z|)
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float th;
-                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z[i]));
-                gq[i] = fmaf(0.5f, th, 0.5f) * gs;
-                if (WITH_LOSS) tile_loss += fmaxf(z[i], 0.f) - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
-              }
-            } else if (LOSS == HASTE_LOSS_BCE && !ragged) {
-              // with positives: dLoss/dz = sigmoid(z) - y, loss = max(z,0) - y z - ln(0.5 + 0.5 |tanh(z/2)|)
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float y = static_cast<float>((ym8 >> i) & 1u);
-                float th;
-                asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z[i]));
-                gq[i] = (fmaf(0.5f, th, 0.5f) - y) * gs;
-                if (WITH_LOSS) tile_loss += fmaxf(z[i], 0.f) - y * z[i] - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
-              }
-            } else if (LOSS == HASTE_LOSS_SQHINGE && !ragged) {
-              // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float ns = __uint_as_float(0x3F800000u | (((ym8 >> i) & 1u) << 31));
-                const float m = fmaxf(fmaf(ns, z[i], 1.f), 0.f);
-                gq[i] = (ns * m) * gs2;
-                if (WITH_LOSS) tile_loss = fmaf(m, m, tile_loss);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float la = 0.f;
-                float gl = loss_grad<LOSS, WITH_LOSS>(z[i], (ym8 >> i) & 1u, la);
-                if (ragged && col0 + c16 + e8 + i >= rows_real) { gl = 0.f; la = 0.f; }
+                const float zr = round_bf16_as_f32(__uint_as_float(r[e8 + i]) + bias8[i]);
+                const uint32_t pos = (ym16 >> (e8 + i)) & 1u;
+                float gl, la;
+                if (LOSS == HASTE_LOSS_SQHINGE) {
+                  // squared hinge with target sign s: dLoss/dz = -2 s max(0, 1 - s z); ns = -s is built from the target bit
+                  const float ns = __uint_as_float(0x3F800000u | (pos << 31));
+                  const float m = fmaxf(fmaf(ns, zr, 1.f), 0.f);
+                  gl = (ns * m) * gs2;
+                  la = m * m;
+                } else {
+                  // dLoss/dz = sigmoid(z) - y, loss = max(z,0) - y z - ln(0.5 + 0.5 |tanh(z/2)|)
+                  const float y = static_cast<float>(pos);
+                  float th;
+                  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * zr));
+                  gl = (fmaf(0.5f, th, 0.5f) - y) * gs;
+                  la = fmaxf(zr, 0.f) - y * zr - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
+                }
+                if (e8 + i >= nvalid) { gl = 0.f; la = 0.f; }
                 if (WITH_LOSS) tile_loss += la;
-                gq[i] = gl * gs;
+                x[i] = gl;
+                if (DEBUG) {
+                  if (a.z_dump != nullptr && row_valid && e8 + i < nvalid)
+                    reinterpret_cast<uint16_t*>(a.z_dump)[(b0 + row) * a.ldz + static_cast<int64_t>(g) * G + col0 + c16 + e8 + i] =
+                        static_cast<uint16_t>(__float_as_uint(zr) >> 16);
+                }
               }
+              const int chunk = ((col0 & 63) + c16 + e8) >> 3;
+              *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) =
+                  make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
             }
-            if (DEBUG) {
-              if (a.z_dump != nullptr && row_valid) {
-                uint16_t* zd = reinterpret_cast<uint16_t*>(a.z_dump) + (b0 + row) * a.ldz + static_cast<int64_t>(g) * G + col0 + c16 + e8;
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (col0 + c16 + e8 + i < rows_real) zd[i] = static_cast<uint16_t>(__float_as_uint(z[i]) >> 16);
-              }
-            }
-            const int chunk = ((col0 & 63) + c16 + e8) >> 3;       // 16-byte chunk inside the 128-byte row of this block
-            *reinterpret_cast<uint4*>(ytile + ((chunk ^ (row & 7)) << 4)) =
-                relu ? make_uint4(pack_bf16x2_relu(gq[0], gq[1]), pack_bf16x2_relu(gq[2], gq[3]), pack_bf16x2_relu(gq[4], gq[5]), pack_bf16x2_relu(gq[6], gq[7]))
-                     : make_uint4(pack_bf16x2(gq[0], gq[1]), pack_bf16x2(gq[2], gq[3]), pack_bf16x2(gq[4], gq[5]), pack_bf16x2(gq[6], gq[7]));
           }
         }
         tc_fence_before();                             // this warp's half of the Z stage has been read
@@ -496,7 +526,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         if (es == 0 && lane == 0) TR(2 + 4 * set, 2700 + it);
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_YFULL + zs));
+        if (lane == 0) mbar_arrive(bar(B_YFULL + ys));
         if (es == 0 && lane == 0) TR(2 + 4 * set, 3000 + it);
       }
       __syncwarp();
@@ -507,94 +537,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       for (int o = 16; o > 0; o >>= 1) loss_acc += __shfl_xor_sync(0xffffffffu, loss_acc, o);
       if (lane == 0 && !*abort_flag) atomicAdd(a.loss, loss_acc * a.grad_scale);
     }
-  } else if (warp >= 4 + N_EA) {
+  } else if (warp >= 4 + N_EA && warp < 4 + N_EA + N_EB) {
     // ================================================================ epilogue B: dXg scatter
     const int q = warp & 3;
     const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
     const int bt = tid - (4 + N_EA) * 32;        // 0..127
-    const int kh = (warp - (4 + N_EA)) >> 2;     // which part of the 64 slots this warp scatters and updates
-    // Weight / bias update of one finished group from its dW accumulator: warp (q, kh) owns label rows
-    // q*32..q*32+31 and slots kh*EB_SLOTS.. in pieces of 16 (two Philox calls each in the packed stream).  These
-    // warps have time to spare between scatters, and the group's accumulator is handed back to the tensor core
-    // as soon as it has been read.
-    auto update_group = [&](int gu) {
-      const int gg = blockIdx.x + gu * gridDim.x;
-      const int wsu = gu & 1;
-      const int64_t l0 = static_cast<int64_t>(gg) * G;
-      const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
-      if (bt == 0) TR(3, 4000 + gu);
-      mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
-      if (bt == 0) TR(3, 4500 + gu);
-      tc_fence_after();
-      const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
-#pragma unroll 1
-      for (int cq = kh * (EB_SLOTS / 16); cq < (kh + 1) * (EB_SLOTS / 16); ++cq) {
-      uint32_t r[16], rb[8];
-      __syncwarp();
-      tmem_ld16(tdw + cq * 16, r);
-      if (HAS_BIAS && cq == 0) tmem_ld8(tdw + F, rb);
-      tmem_ld_wait();
-      if (cq == (kh + 1) * (EB_SLOTS / 16) - 1) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
-      }
-      if (row < rows_real_u && !*abort_flag) {
-        const int64_t l = l0 + row, gl = u.label0 + l;
-        const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
-        __nv_bfloat16* wrow = u.w + l * F;
-        const uint8_t* wsm = sm + OFF_W + wsu * WSTAGE + row * 128;   // the group's W tile still holds the old weights
-        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
-        if (sr) {
-          if (packed) {
-            const uint4 rp0 = rand_packed8(u.seed, u.step, gl, cq * 2), rp1 = rand_packed8(u.seed, u.step, gl, cq * 2 + 1);
-            rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
-            rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
-          } else {
-#pragma unroll
-            for (int x = 0; x < 16; x += 2)
-              rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + cq * 16 + x) | (rand16_reference_call(u.seed, gl * F + cq * 16 + x + 1) << 16);
-          }
-        }
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int c8 = cq * 2 + hf;
-          const uint4 wv = *reinterpret_cast<const uint4*>(wsm + ((c8 ^ (row & 7)) << 4));
-          const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
-          uint32_t ob[4];
-#pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const float a0 = __uint_as_float(r[hf * 8 + 2 * p]), a1 = __uint_as_float(r[hf * 8 + 2 * p + 1]);
-            // the gradient is first rounded to bf16, as the unfused kernel would store it
-            const uint32_t gp = pack_bf16x2(a0, a1);
-            if (DEBUG) { if (a.dw_dump != nullptr) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + c8 * 8)[p] = gp; }
-            const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
-            const float w0 = __uint_as_float(wp[p] << 16), w1 = __uint_as_float(wp[p] & 0xFFFF0000u);
-            float n0, n1;
-            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
-            const uint32_t rr = rnd[hf * 4 + p];
-            const uint32_t o0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
-            const uint32_t o1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
-            ob[p] = (o0 & 0xFFFFu) | (o1 << 16);
-          }
-          *reinterpret_cast<uint4*>(wrow + c8 * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-        }
-        if (HAS_BIAS && cq == 0) {
-          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
-          if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
-          uint32_t r16 = 0;
-          if (sr) r16 = rand16(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
-          // the old bias comes from the group's bias row in shared memory (the fp32 image of the bf16 value: exact)
-          const uint16_t b_old = __bfloat16_as_ushort(__float2bfloat16_rn(bias_s[wsu * G + row]));
-          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(b_old, gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
-        }
-      }
-      }
-      __syncwarp();
-      if (bt == 0) TR(3, 6000 + gu);
-      if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / index row / bias row
-    };
+    const int kh = (warp - (4 + N_EA)) >> 2;     // which half of the 64 slots this warp scatters
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int ws = gi & 1;
@@ -628,7 +576,115 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         }
         if (bt == 0) TR(3, 2000 + it);
       }
-      update_group(gi);                          // ends with this warp's arrival on the group's MEMPTY barrier
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_MEMPTY + ws));    // this warp no longer needs the group's index row
+    }
+  } else {
+    // ================================================================ update warps: SGD + stochastic rounding
+    // Weight / bias update of each finished group from its dW accumulator: warp (q, kh) owns label rows
+    // q*32..q*32+31 and slots kh*32..kh*32+31.  The accumulator slice is read, rounded to bf16 (as the unfused
+    // kernel would store the gradient) and handed back to the tensor core at once; the old weights and bias are
+    // copied out of the group's W tile / bias row in shared memory and the stage is released; only then does the
+    // slow part (Philox, update arithmetic, stores) run, holding nothing the pipeline needs.
+    const int q = warp & 3;
+    const int row = q * 32 + lane;               // label row inside the group == TMEM lane
+    const int kh = (warp - (4 + N_EA + N_EB)) >> 2;
+    static_assert(UP_SLOTS == 32, "two 16-slot pieces per update warp");
+    for (int gu = 0; gu < n_my_groups; ++gu) {
+      const int gg = blockIdx.x + gu * gridDim.x;
+      const int wsu = gu & 1;
+      const int64_t l0 = static_cast<int64_t>(gg) * G;
+      const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
+      mbar_wait(bar(B_WFULL + wsu), (gu >> 1) & 1, abort_flag, a.err, 15, WAIT_LIMIT);   // W tile and bias row are in place
+      if (warp == 4 + N_EA + N_EB && lane == 0) TR(6, 4000 + gu);
+      mbar_wait(bar(B_DWFULL), gu & 1, abort_flag, a.err, 13, WAIT_LIMIT);
+      if (warp == 4 + N_EA + N_EB && lane == 0) TR(6, 4500 + gu);
+      tc_fence_after();
+      const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW;
+      uint32_t gw[16];                            // this thread's 32 gradients, bf16 pairs
+      float gb = 0.f;
+      {
+        uint32_t r_lo[16], r_hi[16], rb[8];
+        __syncwarp();
+        tmem_ld16(tdw + kh * UP_SLOTS, r_lo);
+        tmem_ld16(tdw + kh * UP_SLOTS + 16, r_hi);
+        if (HAS_BIAS && kh == 0) tmem_ld8(tdw + F, rb);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_DWEMPTY));
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          gw[x] = pack_bf16x2(__uint_as_float(r_lo[2 * x]), __uint_as_float(r_lo[2 * x + 1]));
+          gw[8 + x] = pack_bf16x2(__uint_as_float(r_hi[2 * x]), __uint_as_float(r_hi[2 * x + 1]));
+        }
+        if (HAS_BIAS && kh == 0) gb = round_to_bf16_f(__uint_as_float(rb[0]));
+      }
+      uint32_t ww[16];                            // the same 32 old weights
+      {
+        const uint8_t* wsm = sm + OFF_W + wsu * WSTAGE + row * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(wsm + (((kh * 4 + c) ^ (row & 7)) << 4));
+          ww[4 * c] = wv.x; ww[4 * c + 1] = wv.y; ww[4 * c + 2] = wv.z; ww[4 * c + 3] = wv.w;
+        }
+      }
+      // the old bias comes from the group's bias row (the fp32 image of the bf16 value: exact)
+      const uint16_t b_old = (HAS_BIAS && kh == 0) ? __bfloat16_as_ushort(__float2bfloat16_rn(bias_s[wsu * G + row])) : uint16_t(0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_MEMPTY + wsu));   // this warp no longer needs the group's W tile / bias row
+      if (row < rows_real_u && !*abort_flag) {
+        const int64_t l = l0 + row, gl = u.label0 + l;
+        const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
+        __nv_bfloat16* wrow = u.w + l * F;
+        if (DEBUG) {
+          if (a.dw_dump != nullptr) {
+#pragma unroll
+            for (int x = 0; x < 16; ++x) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + kh * UP_SLOTS)[x] = gw[x];
+          }
+        }
+#pragma unroll 1
+        for (int pc = 0; pc < 2; ++pc) {          // two pieces of 16 slots (two Philox calls each in the packed stream)
+          const int cq = kh * 2 + pc;
+          uint32_t g8[8], w8[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) { g8[x] = pc ? gw[8 + x] : gw[x]; w8[x] = pc ? ww[8 + x] : ww[x]; }
+          uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
+          if (sr) {
+            if (packed) {
+              const uint4 rp0 = rand_packed8_call(u.seed, u.step, gl, cq * 2), rp1 = rand_packed8_call(u.seed, u.step, gl, cq * 2 + 1);
+              rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
+              rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
+            } else {
+#pragma unroll
+              for (int x = 0; x < 16; x += 2)
+                rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + cq * 16 + x) | (rand16_reference_call(u.seed, gl * F + cq * 16 + x + 1) << 16);
+            }
+          }
+          uint32_t ob[8];
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            const float g0 = __uint_as_float(g8[p] << 16), g1 = __uint_as_float(g8[p] & 0xFFFF0000u);
+            const float w0 = __uint_as_float(w8[p] << 16), w1 = __uint_as_float(w8[p] & 0xFFFF0000u);
+            float n0, n1;
+            if (contract) { n0 = sgd_math<true>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<true>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            else          { n0 = sgd_math<false>(w0, g0, nullptr, u.lr, u.wd, 0.f); n1 = sgd_math<false>(w1, g1, nullptr, u.lr, u.wd, 0.f); }
+            const uint32_t rr = rnd[p];
+            const uint32_t o0 = sr ? ((__float_as_uint(n0) + (rr & 0xFFFFu)) >> 16) : rn_bf16_bits(n0);
+            const uint32_t o1 = sr ? ((__float_as_uint(n1) + (rr >> 16)) >> 16) : rn_bf16_bits(n1);
+            ob[p] = (o0 & 0xFFFFu) | (o1 << 16);
+          }
+          *reinterpret_cast<uint4*>(wrow + cq * 16) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+          *reinterpret_cast<uint4*>(wrow + cq * 16 + 8) = make_uint4(ob[4], ob[5], ob[6], ob[7]);
+        }
+        if (HAS_BIAS && kh == 0) {
+          if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(gb);
+          uint32_t r16 = 0;
+          if (sr) r16 = rand16_call(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl);
+          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(b_old, gb, nullptr, u.lr, u.wd, u.mu, u.flags, r16));
+        }
+      }
+      if (warp == 4 + N_EA + N_EB && lane == 0) TR(6, 6000 + gu);
     }
   }
 

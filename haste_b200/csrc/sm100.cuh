@@ -40,13 +40,11 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 // Bounded wait: gives up after `limit` clock cycles, raises the CTA-wide abort flag and records `code`
 // in *err (host-visible).  Every later wait in the CTA returns at once when the flag is up, so all roles
 // run to the end of their loops and the kernel exits normally.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
-                                          long long limit, unsigned sleep_ns = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ static bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                                  long long limit, unsigned sleep_ns) {
   const long long t0 = clock64();
   for (;;) {
-    // tight polling burst: the abort flag and the clock are looked at only between bursts, so a waiting warp
-    // costs the scheduler a few instructions per poll instead of a dozen
+    // polling burst: the abort flag and the clock are looked at only between bursts
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
@@ -59,6 +57,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+// The first try (which the hardware may hold for a few microseconds while the phase is incomplete) is inline;
+// the bounded polling loop is a call, so that the many wait sites stay small in the instruction cache.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                          long long limit, unsigned sleep_ns = 0) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, err, code, limit, sleep_ns);
 }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -95,6 +100,14 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// One lane of the (converged) warp: the same lane every time for the full mask.  Issuing tcgen05.mma / commit from
+// an elected lane of a warp that runs its control flow converged lets the compiler keep descriptors in uniform
+// registers; the same instructions under "if (lane == 0)" cost several times the code.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}\n" : "=r"(pred));
+  return pred != 0;
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate; one thread issues.
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -150,6 +163,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(r) : "r"(taddr) : "memory");
+  return r;
 }
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
