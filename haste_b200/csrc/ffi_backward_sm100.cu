@@ -179,7 +179,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
     }
   } else if (warp == 1 || warp == 3) {
     // ================================================================ MMA issuers
-    if (lane == 0) {
+    // Each warp runs its control flow converged; one elected lane issues the products and commits (descriptors
+    // stay in uniform registers this way).
+    {
       constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
       constexpr uint32_t ID_BWW = make_idesc(128, FR, 1, 0);
       const uint64_t D_XB = make_sdesc(sbase + OFF_X, 16, 1024);      // X tile as K-major  B   (backward-weights)
@@ -201,15 +203,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
             tc_fence_after();
             const uint32_t ya = ya_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
             const uint32_t tdx = tmem + TM_DX + (ds ? F : 0);
-            umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
+            if (elect_one()) {
+              umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
 #pragma unroll
-            for (int ks = 1; ks < G / 16; ++ks)
-              umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
-            tc_commit(bar(B_DXFULL + ds));
-            tc_commit(bar(B_YEMPTY + ys));
+              for (int ks = 1; ks < G / 16; ++ks)
+                umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
+              tc_commit(bar(B_DXFULL + ds));
+              tc_commit(bar(B_YEMPTY + ys));
+              if (t + 1 == T) tc_commit(bar(B_WEMPTY + ws));
+            }
+            __syncwarp();
             if (++ys == NYS) { ys = 0; yph ^= 1; }
           }
-          tc_commit(bar(B_WEMPTY + ws));
         }
       } else {
         const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
@@ -224,16 +229,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
             mbar_wait(bar(B_YFULL + ys), yph, abort_flag, a.err, 39, WAIT_LIMIT);
             tc_fence_after();
             const uint32_t ym = ym_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
-            umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
+            if (elect_one()) {
+              umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
 #pragma unroll
-            for (int ks = 1; ks < BT / 16; ++ks)
-              umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
-            tc_commit(bar(B_YEMPTY + ys));
-            tc_commit(bar(B_XEMPTY + xs));
+              for (int ks = 1; ks < BT / 16; ++ks)
+                umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
+              tc_commit(bar(B_YEMPTY + ys));
+              tc_commit(bar(B_XEMPTY + xs));
+              if (t + 1 == T) tc_commit(bar(B_DWFULL + (gi & 1)));
+            }
+            __syncwarp();
             if (++xs == NXS) { xs = 0; xph ^= 1; }
             if (++ys == NYS) { ys = 0; yph ^= 1; }
           }
-          tc_commit(bar(B_DWFULL + (gi & 1)));
         }
       }
     }

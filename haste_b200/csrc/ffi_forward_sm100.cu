@@ -145,7 +145,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
-    if (lane == 0) {
+    // The warp runs its control flow converged; one elected lane issues the products and commits (descriptors stay
+    // in uniform registers this way).
+    {
       constexpr uint32_t ID_FWD = make_idesc(128, G, 1, 0);
       const uint64_t D_XA = make_sdesc(sbase + OFF_X, XBLK, 1024);    // X tile as MN-major A
       const uint64_t D_WB = make_sdesc(sbase + OFF_W, 16, 1024);      // W tile as K-major B
@@ -163,15 +165,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
           tc_fence_after();
           const uint32_t xa = xa_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4), wb = wb_lo + (ws ? (WSTAGE >> 4) : 0u);
           const uint32_t tz = tmem + (zs ? G : 0);
-          umma_bf16_lohi<false>(tz, xa, xa_hi, wb, wb_hi, id_fwd);
+          if (elect_one()) {
+            umma_bf16_lohi<false>(tz, xa, xa_hi, wb, wb_hi, id_fwd);
 #pragma unroll
-          for (int ks = 1; ks < F / 16; ++ks)
-            umma_bf16_lohi<true>(tz, xa + ((ks * 2048) >> 4), xa_hi, wb + ((ks * 32) >> 4), wb_hi, id_fwd);
-          tc_commit(bar(B_ZFULL + zs));
-          tc_commit(bar(B_XEMPTY + xs));
+            for (int ks = 1; ks < F / 16; ++ks)
+              umma_bf16_lohi<true>(tz, xa + ((ks * 2048) >> 4), xa_hi, wb + ((ks * 32) >> 4), wb_hi, id_fwd);
+            tc_commit(bar(B_ZFULL + zs));
+            tc_commit(bar(B_XEMPTY + xs));
+            if (t + 1 == T) tc_commit(bar(B_WEMPTY + ws));
+          }
+          __syncwarp();
           if (++xs == NXS) { xs = 0; xph ^= 1; }
         }
-        tc_commit(bar(B_WEMPTY + ws));
       }
     }
   } else if (warp >= 4) {
