@@ -400,11 +400,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
           uint32_t* yb = ybits + (it & 1) * BT * 4;
           for (int i = et; i < BT * 4; i += N_EA_SET * 32) yb[i] = 0u;
           named_bar_sync(1 + set, N_EA_SET * 32);
-          for (int i = t_beg + et; i < t_end; i += N_EA_SET * 32) {
-            const uint32_t e = __ldg(a.tgt_ent + i);
-            const int64_t rb = static_cast<int64_t>(e >> 8) - b0;
-            const int c = e & 0xFF;
-            if (rb >= 0 && rb < BT && c < G) atomicOr(&yb[rb * 4 + (c >> 5)], 1u << (c & 31));
+          // head groups of a long-tailed label distribution hold thousands of entries: eight independent loads in
+          // flight per thread, so that the scan runs at L2 throughput rather than one L2 latency per entry
+          for (int i0 = t_beg + et; i0 < t_end; i0 += 8 * N_EA_SET * 32) {
+            uint32_t e8[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              const int i = i0 + x * N_EA_SET * 32;
+              e8[x] = i < t_end ? __ldg(a.tgt_ent + i) : 0xFFFFFFFFu;       // row 2^24 - 1: outside every tile
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              const int64_t rb = static_cast<int64_t>(e8[x] >> 8) - b0;
+              const int c = e8[x] & 0xFF;
+              if (rb >= 0 && rb < BT && c < G) atomicOr(&yb[rb * 4 + (c >> 5)], 1u << (c & 31));
+            }
           }
           named_bar_sync(1 + set, N_EA_SET * 32);
           if (EA_COLS == 32) ym = yb[row * 4 + h];

@@ -24,6 +24,59 @@ def shard_groups(num_groups, world_size, rank):
     return g0, g0 + base + (1 if rank < rem else 0)
 
 
+def split_groups_by_cost(cost, world_size):
+    """Contiguous split of label groups into ``world_size`` ranges of near-equal total ``cost``.
+
+    ``cost``: one non-negative number per group (sequence or 1-D tensor).  Returns ``world_size + 1`` boundaries
+    ``b`` with ``b[0] = 0``, ``b[-1] = len(cost)``, non-decreasing; rank ``r`` owns groups ``[b[r], b[r+1])``.
+    Boundary ``r`` is placed where the running sum first reaches ``r / world_size`` of the total, so every range
+    is within one group's cost of its fair share.  With uniform cost this is the split of ``shard_groups``
+    up to where the remainder goes.
+    """
+    c = torch.as_tensor(cost, dtype=torch.float64).flatten().clamp_min(0)
+    n = c.numel()
+    if world_size <= 1 or n == 0:
+        return [0] + [n] * max(world_size, 1)
+    total = float(c.sum())
+    if total <= 0:
+        return [shard_groups(n, world_size, r)[0] for r in range(world_size)] + [n]
+    csum = torch.cumsum(c, 0)
+    bounds = [0]
+    for r in range(1, world_size):
+        k = int(torch.searchsorted(csum, torch.tensor(total * r / world_size, dtype=torch.float64)).item())
+        # the group that crosses the mark goes to whichever side leaves the smaller excess
+        if k < n and float(csum[k]) - total * r / world_size <= total * r / world_size - (float(csum[k - 1]) if k > 0 else 0.0):
+            k += 1
+        bounds.append(min(max(k, bounds[-1]), n))
+    bounds.append(n)
+    return bounds
+
+
+def group_cost_from_targets(targets, L, G, B, general_chunk_cost=1.5, bitmap_cost=0.5):
+    """Relative cost of each label group in the fused step, estimated from one batch's COO targets [nnz,2].
+
+    A group costs its batch tiles; a 32-row x 16-label chunk that holds a positive takes the general branch of the
+    loss epilogue (about ``general_chunk_cost`` more than a chunk without), and a group with more than 8 entries
+    builds a shared-memory bitmap per tile (``bitmap_cost`` of a group).  Label frequencies are long-tailed, so a
+    split by group count leaves the rank that owns the head labels well behind the others.
+    """
+    NG = (L + G - 1) // G
+    t = torch.as_tensor(targets).to(torch.int64).cpu()
+    cost = torch.ones(NG, dtype=torch.float64)
+    if t.numel() == 0:
+        return cost
+    row, lab = t[:, 0], t[:, 1]
+    keep = (lab >= 0) & (lab < L)
+    row, lab = row[keep], lab[keep]
+    grp = lab // G
+    chunks_per_group = max(1, ((B + 31) // 32) * (G // 16))
+    chunk_id = grp * chunks_per_group + (row // 32) * (G // 16) + (lab % G) // 16
+    hit = torch.bincount(torch.unique(chunk_id) // chunks_per_group, minlength=NG).to(torch.float64)
+    n_ent = torch.bincount(grp, minlength=NG)
+    cost += general_chunk_cost * hit / chunks_per_group + bitmap_cost * (n_ent > 8).to(torch.float64)
+    return cost
+
+
 def shard_labels(L, G, world_size, rank):
     """Label range [l0, l1) and group range [g0, g1) owned by ``rank`` (whole groups only; the ragged last
     group goes to the last non-empty shard)."""
@@ -112,10 +165,12 @@ class ShardedFFILayer:
     """Label-sharded layer: this rank's ``FusedFFIShard`` plus the dX all-reduce.
 
     ``full_*`` tensors describe the whole layer (on any device); each rank copies its slice to ``device``.
+    ``group_cost`` (optional, one number per label group, identical on every rank) replaces the split by group
+    count with a contiguous split of equal estimated cost; ``group_cost_from_targets`` derives it from a batch.
     """
 
     def __init__(self, full_locations, full_weights, full_bias, group_size, in_features, device, *, process_group=None,
-                 rank=None, world_size=None, **shard_kwargs):
+                 rank=None, world_size=None, group_cost=None, **shard_kwargs):
         import torch.distributed as dist
         self.dist = dist
         self.pg = process_group
@@ -125,7 +180,13 @@ class ShardedFFILayer:
             world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank, self.world = rank, world_size
         L = full_weights.shape[0]
-        l0, l1, g0, g1 = shard_labels(L, group_size, world_size, rank)
+        if group_cost is None:
+            l0, l1, g0, g1 = shard_labels(L, group_size, world_size, rank)
+        else:
+            # contiguous ranges of near-equal estimated cost (every rank must pass the same costs)
+            bounds = split_groups_by_cost(group_cost, world_size)
+            g0, g1 = bounds[rank], bounds[rank + 1]
+            l0, l1 = min(L, g0 * group_size), min(L, g1 * group_size)
         self.l0, self.l1, self.g0, self.g1 = l0, l1, g0, g1
         self.shard = FusedFFIShard(full_locations[g0:g1].to(device).contiguous(), full_weights[l0:l1].to(device).contiguous(),
                                    None if full_bias is None else full_bias[l0:l1].to(device).contiguous(), group_size,
