@@ -76,6 +76,31 @@ def test_shard_partition():
     assert parts[0][0] == 0 and parts[-1][1] == L and all(p[0] % G == 0 for p in parts)
 
 
+def test_split_groups_by_cost():
+    """Cost-weighted contiguous split: a partition, monotone, each range within one group's cost of its share."""
+    import torch
+    from haste_b200.fused import split_groups_by_cost, group_cost_from_targets
+    assert split_groups_by_cost([1] * 10, 1) == [0, 10]
+    assert split_groups_by_cost([0, 0, 0], 2)[0] == 0 and split_groups_by_cost([0, 0, 0], 2)[-1] == 3
+    gen = torch.Generator().manual_seed(5)
+    for n, R in ((1, 4), (7, 2), (100, 8), (5236, 8)):
+        cost = torch.rand(n, generator=gen, dtype=torch.float64) + 0.1
+        cost[0] = 25.0                                    # a heavy head group
+        b = split_groups_by_cost(cost, R)
+        assert len(b) == R + 1 and b[0] == 0 and b[-1] == n and all(x <= y for x, y in zip(b, b[1:]))
+        share = float(cost.sum()) / R
+        for r in range(R):
+            tot = float(cost[b[r]:b[r + 1]].sum())
+            assert tot <= share + float(cost.max()) + 1e-9
+    # the estimate itself: a group full of positives costs more than an empty one, which costs exactly 1
+    L, G, B = 1000, 128, 256
+    rows = torch.arange(B).repeat_interleave(4)
+    labs = torch.arange(4).repeat(B)                      # every row has labels 0..3: all in group 0
+    cost = group_cost_from_targets(torch.stack([rows, labs], 1).to(torch.int32), L, G, B)
+    assert cost.shape == (8,) and cost[0] > 1.0 and torch.all(cost[1:] == 1.0)
+    assert torch.all(group_cost_from_targets(torch.zeros(0, 2, dtype=torch.int32), L, G, B) == 1.0)
+
+
 _WORKER = r"""
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
