@@ -178,43 +178,64 @@ __global__ void tgt_fill_kernel(const int32_t* __restrict__ coo, int64_t nnz, in
 // Block 0 buckets the COO targets entirely in shared memory (count, scan, fill: no global scratch) and clears
 // the loss scalar; every other block transposes one 32x32 tile of x [B,D] -> xt [D,B] and clears the same tile
 // of dxt [D,B].  Replaces one memset, the three bucketing kernels, the transpose and two fills.
-__global__ void __launch_bounds__(256) step_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, float* __restrict__ dxt,
-                                                           float* __restrict__ loss, const int32_t* __restrict__ coo, int64_t nnz,
-                                                           int64_t label0, int64_t L, int G, int NG, int32_t* __restrict__ ptr,
-                                                           uint32_t* __restrict__ ent, int64_t B, int64_t D, int tiles_d) {
+constexpr int PREP_THREADS = 1024;
+__global__ void __launch_bounds__(PREP_THREADS) step_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, float* __restrict__ dxt,
+                                                                    float* __restrict__ loss, const int32_t* __restrict__ coo, int64_t nnz,
+                                                                    int64_t label0, int64_t L, int G, int NG, int32_t* __restrict__ ptr,
+                                                                    uint32_t* __restrict__ ent, int64_t B, int64_t D, int tiles_d) {
   extern __shared__ int32_t cnt[];          // NG counters, then reused as fill cursors
-  __shared__ int part[256];
+  __shared__ int part[PREP_THREADS];
   const int tid = threadIdx.x;
   if (blockIdx.x == 0) {
+    // One block does the whole bucketing, so its two passes over the entries keep four independent 8-byte loads
+    // in flight per thread (a batch of C5 has ~37 K entries; one load at a time costs one L2 latency per entry).
+    const int2* coo2 = reinterpret_cast<const int2*>(coo);
     if (tid == 0 && loss != nullptr) *loss = 0.f;
-    for (int i = tid; i < NG; i += 256) cnt[i] = 0;
+    for (int i = tid; i < NG; i += PREP_THREADS) cnt[i] = 0;
     __syncthreads();
-    for (int64_t i = tid; i < nnz; i += 256) {
-      const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
-      if (c >= 0 && c < L) atomicAdd(&cnt[c / G], 1);
+    for (int64_t i0 = tid; i0 < nnz; i0 += 4 * PREP_THREADS) {
+      int2 e[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { const int64_t i = i0 + k * PREP_THREADS; e[k] = i < nnz ? __ldg(coo2 + i) : make_int2(0, -1); }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t c = static_cast<int64_t>(e[k].y) - label0;
+        if (e[k].y >= 0 && c >= 0 && c < L) atomicAdd(&cnt[c / G], 1);
+      }
     }
     __syncthreads();
     // exclusive scan of cnt[0..NG): each thread owns a contiguous chunk
-    const int chunk = (NG + 255) / 256, lo = min(NG, tid * chunk), hi = min(NG, lo + chunk);
+    const int chunk = (NG + PREP_THREADS - 1) / PREP_THREADS, lo = min(NG, tid * chunk), hi = min(NG, lo + chunk);
     int sum = 0;
     for (int i = lo; i < hi; ++i) sum += cnt[i];
     part[tid] = sum;
     __syncthreads();
-    if (tid == 0) {
-      int run = 0;
-      for (int i = 0; i < 256; ++i) { const int v = part[i]; part[i] = run; run += v; }
-      ptr[NG] = run;
+    if (tid < 32) {                        // warp 0 scans the 1024 partial sums, 32 per lane
+      int loc_sum = 0;
+      for (int i = 0; i < PREP_THREADS / 32; ++i) loc_sum += part[tid * (PREP_THREADS / 32) + i];
+      int incl = loc_sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (tid >= o) incl += v; }
+      int run = incl - loc_sum;
+      for (int i = 0; i < PREP_THREADS / 32; ++i) { const int idx = tid * (PREP_THREADS / 32) + i; const int v = part[idx]; part[idx] = run; run += v; }
+      if (tid == 31) ptr[NG] = run;
     }
     __syncthreads();
     int run = part[tid];
     for (int i = lo; i < hi; ++i) { const int v = cnt[i]; ptr[i] = run; cnt[i] = run; run += v; }   // cnt becomes the write cursor
     __syncthreads();
-    for (int64_t i = tid; i < nnz; i += 256) {
-      const int64_t c = static_cast<int64_t>(coo[2 * i + 1]) - label0;
-      if (c >= 0 && c < L) {
-        const int64_t g = c / G;
-        const int pos = atomicAdd(&cnt[g], 1);
-        ent[pos] = (static_cast<uint32_t>(coo[2 * i]) << 8) | static_cast<uint32_t>(c - g * G);
+    for (int64_t i0 = tid; i0 < nnz; i0 += 4 * PREP_THREADS) {
+      int2 e[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { const int64_t i = i0 + k * PREP_THREADS; e[k] = i < nnz ? __ldg(coo2 + i) : make_int2(0, -1); }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t c = static_cast<int64_t>(e[k].y) - label0;
+        if (e[k].y >= 0 && c >= 0 && c < L) {
+          const int64_t g = c / G;
+          const int pos = atomicAdd(&cnt[g], 1);
+          ent[pos] = (static_cast<uint32_t>(e[k].x) << 8) | static_cast<uint32_t>(c - g * G);
+        }
       }
     }
     return;
@@ -222,28 +243,29 @@ __global__ void __launch_bounds__(256) step_prepare_kernel(const uint16_t* __res
   __shared__ uint16_t tile[32][34];
   const int blk = blockIdx.x - 1;
   const int64_t d0 = static_cast<int64_t>(blk % tiles_d) * 32, b0 = static_cast<int64_t>(blk / tiles_d) * 32;
-  const int tx = tid & 31, ty = tid >> 5;
-  for (int j = ty; j < 32; j += 8) {
-    const int64_t b = b0 + j, d = d0 + tx;
-    tile[j][tx] = (b < B && d < D) ? x[b * D + d] : uint16_t(0);
+  const int tx = tid & 31, ty = tid >> 5;            // 32 x 32 threads: one element each
+  {
+    const int64_t b = b0 + ty, d = d0 + tx;
+    tile[ty][tx] = (b < B && d < D) ? x[b * D + d] : uint16_t(0);
   }
   __syncthreads();
-  for (int j = ty; j < 32; j += 8) {
-    const int64_t d = d0 + j, b = b0 + tx;
-    if (d < D && b < B) { xt[d * B + b] = tile[tx][j]; dxt[d * B + b] = 0.f; }
+  {
+    const int64_t d = d0 + ty, b = b0 + tx;
+    if (d < D && b < B) { xt[d * B + b] = tile[tx][ty]; dxt[d * B + b] = 0.f; }
   }
 }
 
 int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz, int64_t label0, int64_t L,
                         int64_t G, int32_t* ptr, uint32_t* ent, int64_t B, int64_t D, cudaStream_t st) {
   const int64_t NG = (L + G - 1) / G;
+  if (reinterpret_cast<uintptr_t>(coo) & 7) return fail(HASTE_ERR_BAD_ARG, "haste_ffi_step_prepare: the COO target pairs must start on an 8-byte boundary");
   const size_t sm = sizeof(int32_t) * static_cast<size_t>(NG);
   if (sm > 200 * 1024) return fail(HASTE_ERR_TOO_LARGE, "haste_ffi_step_prepare: %lld label groups need more shared memory than one block has; "
                                    "use haste_transpose_bf16 + haste_targets_bucket", (long long)NG);
   cudaError_t e = cudaFuncSetAttribute(step_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
   if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const int tiles_d = static_cast<int>((D + 31) / 32), tiles_b = static_cast<int>((B + 31) / 32);
-  step_prepare_kernel<<<1 + tiles_d * tiles_b, 256, sm, st>>>((const uint16_t*)x, (uint16_t*)xt, dxt, loss, coo, nnz, label0, L, int(G), int(NG),
+  step_prepare_kernel<<<1 + tiles_d * tiles_b, PREP_THREADS, sm, st>>>((const uint16_t*)x, (uint16_t*)xt, dxt, loss, coo, nnz, label0, L, int(G), int(NG),
                                                                ptr, ent, B, D, tiles_d);
   return check_launch("step_prepare_kernel");
 }

@@ -115,7 +115,8 @@ int haste_targets_bucket(const int32_t* coo, int64_t nnz, int64_t label0, int64_
 
 /* Everything the fused step needs per batch, in one launch: xt = transpose(x [B,D] bf16), dxt cleared, *loss
  * cleared (loss may be NULL), and the COO targets bucketed as by haste_targets_bucket (counters live in shared
- * memory, so no scratch argument; at most ~51,000 label groups — HASTE_ERR_TOO_LARGE beyond).
+ * memory, so no scratch argument; at most ~51,000 label groups — HASTE_ERR_TOO_LARGE beyond).  `coo` must be
+ * 8-byte aligned (any row of an int32 [nnz,2] tensor is).
  * Replaces the transpose of shared_ffi/bindings.py:19 and the per-step zero fills. */
 int haste_ffi_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz,
                            int64_t label0, int64_t L, int64_t G, int32_t* tgt_ptr, uint32_t* tgt_ent,
