@@ -1,6 +1,7 @@
 // Fused FFI train step on the 5th-generation tensor cores (tcgen05 + TMEM), group size 128, fan-in 64.
 //
-// One persistent CTA per SM walks label groups g = blockIdx.x, += gridDim.x.  Per group and per 128-row
+// One persistent CTA per SM walks label groups g = blockIdx.x, += gridDim.x (the incomplete last round goes to the
+// highest-numbered CTAs).  Per group and per 128-row
 // batch tile three UMMA products run out of the same three shared-memory tiles (none is ever transposed or
 // re-gathered; the 128-byte-swizzled "row block" layout serves both operand majors):
 //     X tile [F rows = slots][128 batch]   gathered rows of xt           (+ one row of ones: bias gradient)
@@ -177,7 +178,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
 
   int tr_n = 0;   // trace cursor of this thread (development builds)
   (void)tr_n;
-  const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+  // Groups are dealt round-robin; the incomplete last round goes to the highest-numbered CTAs.  The head of a
+  // long-tailed label distribution sits in the first groups, whose tiles are the expensive ones (positives, target
+  // bitmap): the CTAs that own them then have one group less to do.
+  const int n_cta = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  const int full_rounds = a.NG / n_cta, rem_groups = a.NG - full_rounds * n_cta;
+  const int n_my_groups = full_rounds + (cta >= n_cta - rem_groups ? 1 : 0);
+  auto group_of = [&](int gi) { return gi < full_rounds ? cta + gi * n_cta : full_rounds * n_cta + (cta - (n_cta - rem_groups)); };
 
   if (warp == 0 || warp == 2) {
     // ================================================================ producers
@@ -194,7 +201,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
       if (lane == 0) mbar_arrive(full_bar);
     };
     for (int gi = 0; gi < n_my_groups; ++gi) {
-      const int g = blockIdx.x + gi * gridDim.x;
+      const int g = group_of(gi);
       const int ws = gi & 1;
       const int64_t l0 = static_cast<int64_t>(g) * G;
       const int rows_real = static_cast<int>(imin64(G, a.L - l0));
@@ -376,7 +383,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     int it = 0, ys = 0, yph = 0;                 // global tile counter, its dY stage and phase
     auto next_tile = [&]() { ++it; if (++ys == NYS) { ys = 0; yph ^= 1; } };
     for (int gi = 0; gi < n_my_groups; ++gi) {
-      const int g = blockIdx.x + gi * gridDim.x;
+      const int g = group_of(gi);
       const int ws = gi & 1;
       const int rows_real = static_cast<int>(imin64(G, a.L - static_cast<int64_t>(g) * G));
       const int t_beg = __ldg(a.tgt_ptr + g), t_end = __ldg(a.tgt_ptr + g + 1);
@@ -601,7 +608,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
     const int kh = (warp - (4 + N_EA + N_EB)) >> 2;
     static_assert(UP_SLOTS == 32, "two 16-slot pieces per update warp");
     for (int gu = 0; gu < n_my_groups; ++gu) {
-      const int gg = blockIdx.x + gu * gridDim.x;
+      const int gg = group_of(gu);
       const int wsu = gu & 1;
       const int64_t l0 = static_cast<int64_t>(gg) * G;
       const int rows_real_u = static_cast<int>(imin64(G, a.L - l0));
