@@ -441,7 +441,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         const float gs2 = 2.f * gs;
         const float inv_gs2_sq = row_valid ? inv_4gs2_sq : 0.f;
         const bool ragged = col0 + EA_COLS > rows_real;     // only the last group of the layer can be ragged
-        float tile_loss = 0.f, fast_loss = 0.f;
+        float tile_loss = 0.f, fast_loss = 0.f;        // fast_loss: hinge (4s)^2-scaled squares, or BCE raw log2 terms
+        const float hgs = 0.5f * gs;
         // 16 label columns per iteration.  Nearly every chunk has no positive label in the warp's 32 rows and no
         // ragged edge: one warp vote per chunk sends those down a branch with no per-element tests (which would cost
         // about a quarter of the epilogue's instructions); the rest take the general branch with target bits and a
@@ -479,16 +480,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
                 }
                 pk = make_uint4(pack_bf16x2_relu(x[0], x[1]), pack_bf16x2_relu(x[2], x[3]), pack_bf16x2_relu(x[4], x[5]), pack_bf16x2_relu(x[6], x[7]));
               } else {
-                // dLoss/dz = sigmoid(z) = 0.5 + 0.5 tanh(z/2) (one MUFU op); loss term softplus(z) =
-                // max(z,0) - ln(0.5 + 0.5 |tanh(z/2)|), whose logarithm argument stays in [0.5, 1]
+                // dLoss/dz = s sigmoid(z) = s/2 + s/2 tanh(z/2) (one MUFU op, one fma); loss term softplus(z) =
+                // max(z,0) - ln 2 * log2(0.5 + 0.5 |tanh(z/2)|), whose logarithm argument stays in [0.5, 1]; the
+                // log2 values are summed raw and scaled by -ln 2 once per tile.
                 float x[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float zr = round_bf16_as_f32(z[i]);
                   float th;
                   asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * zr));
-                  x[i] = fmaf(0.5f, th, 0.5f) * gs;
-                  if (WITH_LOSS) tile_loss += fmaxf(zr, 0.f) - 0.69314718f * __log2f(fmaf(0.5f, fabsf(th), 0.5f));
+                  x[i] = fmaf(hgs, th, hgs);
+                  if (WITH_LOSS) { tile_loss += fmaxf(zr, 0.f); fast_loss += __log2f(fmaf(0.5f, fabsf(th), 0.5f)); }
                 }
                 pk = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
               }
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
         tc_fence_before();                             // this warp's half of the Z stage has been read
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
-        if (WITH_LOSS && row_valid) loss_acc += tile_loss + fast_loss * inv_gs2_sq;
+        if (WITH_LOSS && row_valid) loss_acc += tile_loss + fast_loss * (LOSS == HASTE_LOSS_SQHINGE ? inv_gs2_sq : -0.69314718f);
         if (es == 0 && lane == 0) TR(2 + 4 * set, 2700 + it);
         fence_proxy_async();
         __syncwarp();
