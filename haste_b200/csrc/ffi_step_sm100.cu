@@ -681,6 +681,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_train_step_sm100_kernel(StepA
             }
           }
           uint32_t ob[8];
+          if (sr && contract) {
+            // the configuration every benchmark and the reference's compiled kernel use, without per-element flag
+            // tests: w' = fma(-lr, fma(wd, w, g), w), then add 16 random bits and keep the high half
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              const float g0 = __uint_as_float(g8[p] << 16), g1 = __uint_as_float(g8[p] & 0xFFFF0000u);
+              const float w0 = __uint_as_float(w8[p] << 16), w1 = __uint_as_float(w8[p] & 0xFFFF0000u);
+              const float n0 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w0, g0), w0), n1 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w1, g1), w1);
+              const uint32_t rr = rnd[p];
+              const uint32_t s0 = __float_as_uint(n0) + (rr & 0xFFFFu), s1 = __float_as_uint(n1) + (rr >> 16);
+              ob[p] = __byte_perm(s0, s1, 0x7632);              // high halves: s0 -> low 16 bits, s1 -> high 16 bits
+            }
+          } else
 #pragma unroll
           for (int p = 0; p < 8; ++p) {
             const float g0 = __uint_as_float(g8[p] << 16), g1 = __uint_as_float(g8[p] & 0xFFFF0000u);
