@@ -312,7 +312,8 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "samples/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step_scaled"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']}"},
+            "config": {"workload": f"{args.workload}: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']} "
+                                   f"SR-SGD lr={LR} wd={WD} momentum=0 rng=packed"},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
