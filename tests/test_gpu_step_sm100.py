@@ -149,3 +149,36 @@ def test_sm100_backward_both(hb, shape):
         _close(dxt, want_x, 1e-2, 1e-3 * max(1.0, float(want_x.abs().max())), "dXt")
         _close(dw, want_w, 1e-2, 1e-3 * max(1.0, float(want_w.abs().max())), "dW")
         _close(db, dY.float().sum(0), 1e-2, 2e-2, "dbias")
+
+
+@pytest.mark.parametrize("loss", ["squared_hinge", "bce"])
+def test_sm100_step_rank_count_independent(hb, loss):
+    """A layer split over ranks (contiguous group ranges of equal estimated cost) must give bit-identical weights
+    and bias to the unsplit layer — random bits are drawn by global label — and the same dX up to the fp32
+    summation order.  The ranks are run one after the other on this GPU; their dX are added on the host."""
+    from haste_b200.fused import FusedFFIShard, group_cost_from_targets, split_groups_by_cost
+    B, D, L = 256, 256, 128 * 37 + 50
+    inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=11, bias_zero=False)
+    X, coo = inp["X"].cuda(), inp["targets"].cuda()
+    kw = dict(loss=loss, lr=0.05, weight_decay=1e-4, seed=123, rng="packed", grad_scale=0.5)
+
+    def run(g0, g1):
+        l0, l1 = min(L, g0 * G), min(L, g1 * G)
+        sh = FusedFFIShard(inp["loc"][g0:g1].cuda().contiguous(), inp["W"][l0:l1].cuda().contiguous(),
+                           inp["bias"][l0:l1].cuda().contiguous(), G, D, label0=l0, **kw)
+        for _ in range(2):                                    # two steps: the second sees updated weights
+            dxt, ls = sh.step(X, coo)
+        torch.cuda.synchronize()
+        return sh.w.clone(), sh.bias.clone(), dxt.clone(), float(ls)
+
+    NG = (L + G - 1) // G
+    w_all, b_all, dxt_all, loss_all = run(0, NG)
+    cost = group_cost_from_targets(inp["targets"], L, G, B)
+    bounds = split_groups_by_cost(cost, 3)
+    assert bounds[0] == 0 and bounds[-1] == NG
+    parts = [run(bounds[r], bounds[r + 1]) for r in range(3)]
+    assert np.array_equal(_bits(torch.cat([p[0] for p in parts])), _bits(w_all))
+    assert np.array_equal(_bits(torch.cat([p[1] for p in parts])), _bits(b_all))
+    dxt_sum = sum(p[2] for p in parts)
+    _close(dxt_sum, dxt_all, 1e-4, 1e-5 * float(dxt_all.abs().max()), "dX summed over ranks")
+    assert abs(sum(p[3] for p in parts) - loss_all) <= 1e-4 * abs(loss_all) + 1e-6
