@@ -239,14 +239,19 @@ def train_step(loc, X, W, bias, targets, G, loss_kind, lr, wd, seed, step=0, gra
 
 
 # --------------------------------------------------------------------------- rewire
-def rewire_scores(W, G, NG):
-    """score[g,k] = (sum over the group's real rows, in row order, of |w| in fp32) / row count
-    (rewire.py:166-185).  Sequential fp32 accumulation so a kernel can reproduce it bit for bit."""
+def rewire_scores(W, G, NG, score_mode='mean'):
+    """'mean': score[g,k] = (sum over the group's real rows, in row order, of |w| in fp32) / row count
+    (rewire.py:166-185; src/group_fanin_real.py:207-226).  Sequential fp32 accumulation so a kernel can
+    reproduce it bit for bit.  'max': score[g,k] = max over the group's real rows of |w|
+    (src/group_fanin_real.py:213-220)."""
     L, F = W.shape
     a = W.float().abs().numpy()
     scores = np.zeros((NG, F), np.float32)
     for g in range(NG):
         rows = a[g * G:min(L, (g + 1) * G)]
+        if score_mode == 'max':
+            scores[g] = rows.max(axis=0)
+            continue
         acc = np.zeros(F, np.float32)
         for r in rows:
             acc = acc + r
@@ -254,12 +259,22 @@ def rewire_scores(W, G, NG):
     return scores
 
 
-def prune_mask(scores, prune_mode, rewire_fraction=None, rewire_threshold=None):
+def prune_mask(scores, prune_mode, rewire_fraction=None, rewire_threshold=None, prune_scope='group'):
     """rewire.py:187-204.  'fraction': the k = int(F*fraction) lowest scores per group, ties
-    broken by lowest slot index (the reference leaves tie order to torch.topk)."""
+    broken by lowest slot index (the reference leaves tie order to torch.topk).
+    prune_scope 'global' (src/group_fanin_real.py:232-250): the k = int(NG*F*fraction) lowest scores of the
+    whole layer, ties broken by lowest flat (group, slot) index."""
     NG, F = scores.shape
     if prune_mode == 'threshold':
         return scores < np.float32(rewire_threshold)
+    if prune_scope == 'global':
+        k = int(NG * F * rewire_fraction)
+        mask = np.zeros(NG * F, bool)
+        if k > 0:
+            flat = scores.reshape(-1)
+            order = np.lexsort((np.arange(NG * F), flat))                  # by score, then flat index
+            mask[order[:k]] = True
+        return mask.reshape(NG, F)
     k = int(F * rewire_fraction)
     mask = np.zeros((NG, F), bool)
     if k == 0:
@@ -286,7 +301,7 @@ def regrow_init_value(seed, step, l, k, F):
 
 def rewire(W, loc, G, D, prune_mode, rewire_fraction=None, rewire_threshold=None,
            init_mode='zero', regrow='unused', regroup=True, seed=0, step=0,
-           injected=None, momentum=None, group0=0):
+           injected=None, momentum=None, group0=0, score_mode='mean', prune_scope='group'):
     """Prune + regrow (+ regroup).  Returns (W_new bf16, loc_new int32, momentum_new).
 
     regrow:
@@ -301,8 +316,8 @@ def rewire(W, loc, G, D, prune_mode, rewire_fraction=None, rewire_threshold=None
     """
     L, F = W.shape
     NG = loc.shape[0]
-    scores = rewire_scores(W, G, NG)
-    mask = prune_mask(scores, prune_mode, rewire_fraction, rewire_threshold)
+    scores = rewire_scores(W, G, NG, score_mode)
+    mask = prune_mask(scores, prune_mode, rewire_fraction, rewire_threshold, prune_scope)
     Wb = _bf16_to_bits(W).copy().reshape(L, F)
     locn = loc.numpy().astype(np.int32).copy()
     mom = momentum.numpy().copy() if momentum is not None else None

@@ -9,6 +9,7 @@ What runs:
   installed Triton rejects the literal ``& -65536`` on an unsigned value (sr_triton.py:13), so a
   scratch copy in a temp dir gets that one token rewritten as ``& 0xFFFF0000`` (same bits); the
   reference tree itself is never modified and no reference source is stored in this repository.
+* src/group_fanin_real.py's GroupFixedFanInReal.rewire (global-fraction pruning, mean / max scores) likewise
 * shared_ffi/rewire.py's GroupFixedFanIn.rewire on CPU tensors, with ``shared_ffi._C`` stubbed
   (the CUDA extension is not needed for rewire) and ``torch.randint`` replaced by a recorded
   index stream so the draw is reproducible without torch's generator.
@@ -118,8 +119,53 @@ def gen_rewire(ref):
                  w1=bf16_bits(layer.weights.detach()), loc1=layer.group_locations.numpy())
 
 
+def gen_rewire_real(ref):
+    """src/group_fanin_real.py's GroupFixedFanInReal.rewire on CPU tensors (global-fraction pruning, mean / max
+    scores), with ``shared_ffi`` stubbed (rewire needs no kernel) and ``torch.randint`` replaced by a recorded
+    stream.  Inputs are checked to be tie-free at the selection boundary, where torch.topk's order is unspecified."""
+    pkg = types.ModuleType("shared_ffi")
+    pkg.ops = types.ModuleType("shared_ffi.ops")
+    sys.modules["shared_ffi"] = pkg
+    sys.modules["shared_ffi.ops"] = pkg.ops
+    spec = importlib.util.spec_from_file_location("ref_group_fanin_real", os.path.join(ref, "src", "group_fanin_real.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    real_randint = torch.randint
+    for name, (D, L, F, G, mode, frac, thr, score) in {
+        "gfrac_mean": (96, 150, 32, 32, "fraction", 0.2, None, "mean"),
+        "gfrac_max": (300, 200, 48, 64, "fraction", 0.1, None, "max"),
+        "thr_max": (96, 70, 16, 16, "threshold", None, 0.17, "max"),
+    }.items():
+        torch.manual_seed(13)
+        layer = mod.GroupFixedFanInReal(D, L, F, bias=True, dtype=torch.bfloat16, group_size=G, prune_mode=mode,
+                                        rewire_fraction=frac, rewire_threshold=thr, init_mode="zero", score_mode=score)
+        w0 = layer.weights.detach().clone()
+        loc0 = layer.group_locations.clone()
+        rs = np.random.RandomState(6)
+        stream = rs.randint(0, D, size=loc0.numel()).astype(np.int32)
+        used = {}
+
+        def fake_randint(*a, **k):
+            size = k.get("size", a[-1] if a else None)
+            n = int(size[0])
+            used["n"] = n
+            return torch.from_numpy(stream[:n].copy()).to(k.get("dtype", torch.int64))
+
+        torch.randint = fake_randint
+        try:
+            layer.rewire()
+        finally:
+            torch.randint = real_randint
+        np.savez(os.path.join(HERE, f"rewire_real_{name}.npz"), D=D, L=L, F=F, G=G, mode=mode, score=score,
+                 frac=-1.0 if frac is None else frac, thr=-1.0 if thr is None else thr,
+                 w0=bf16_bits(w0), loc0=loc0.numpy(), injected=stream[:used.get("n", 0)],
+                 w1=bf16_bits(layer.weights.detach()), loc1=layer.group_locations.numpy())
+
+
 if __name__ == "__main__":
     ref = sys.argv[1]
     gen_sr(ref)
     gen_rewire(ref)
+    gen_rewire_real(ref)
     print("golden vectors written to", HERE)

@@ -70,6 +70,28 @@ def test_rewire_matches_reference(golden_dir, name):
     assert not np.array_equal(z["loc0"], z["loc1"])          # the case actually rewired something
 
 
+@pytest.mark.parametrize("name", ["gfrac_mean", "gfrac_max", "thr_max"])
+def test_rewire_global_matches_reference(golden_dir, name):
+    """Global-fraction pruning and max scores against src/group_fanin_real.py:149-286 (run on CPU with injected
+    indices).  torch.topk leaves the order of equal scores open, so the case must be tie-free at the selection
+    boundary for the comparison to mean anything: that is asserted first."""
+    z = np.load(os.path.join(golden_dir, f"rewire_real_{name}.npz"))
+    W0, loc0 = _bf16(z["w0"]), torch.from_numpy(z["loc0"].copy())
+    mode, score = str(z["mode"]), str(z["score"])
+    NG, F = loc0.shape
+    if mode == "fraction":
+        sc = np.sort(fo.rewire_scores(W0, int(z["G"]), NG, score).reshape(-1))
+        k = int(NG * F * float(z["frac"]))
+        assert 0 < k < sc.size and sc[k - 1] < sc[k], "golden case has a tie at the selection boundary"
+    W1, loc1, _ = fo.rewire(W0, loc0, int(z["G"]), int(z["D"]), mode,
+                            rewire_fraction=float(z["frac"]) if mode == "fraction" else None,
+                            rewire_threshold=float(z["thr"]) if mode == "threshold" else None,
+                            init_mode="zero", regroup=False, injected=z["injected"], score_mode=score, prune_scope="global")
+    assert np.array_equal(loc1.numpy(), z["loc1"])
+    assert np.array_equal(fo._bf16_to_bits(W1), z["w1"])
+    assert not np.array_equal(z["loc0"], z["loc1"])
+
+
 def test_sr_unbiased():
     # E[round(w)] = w within 3 sigma over 1e6 draws, both random streams.
     w = np.float32(0.1234567)
