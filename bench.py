@@ -352,6 +352,7 @@ def run_aux(args):
     g = torch.randn(L, F, device=dev).to(torch.bfloat16)
     mom = torch.zeros(L, F, device=dev)
     w2 = W.clone()
+    rw_scratch = torch.empty(hffi.rewire_scratch_words(NG, F), dtype=torch.int32, device=dev)
     rows = [
         ("ffi_forward (unfused, writes Z)", lambda: hffi.forward(loc, xt, W, bias, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_features (unfused, reads dY)", lambda: hffi.backward_features(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
@@ -362,6 +363,10 @@ def run_aux(args):
         ("sgd_sr_update reference stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="reference")), 6 * L * F),
         ("sgd_sr_update packed + momentum", lambda: hffi.sgd_sr_update(w2, g, mom, 0, LR, WD, 0.9, SEED, 1, hffi.make_flags(rng="packed")), 14 * L * F),
         ("rewire fraction 0.15, unused regrow, zero init, regroup", lambda: hffi.rewire(w2, loc, None, D, G, 0, 1, 0.0, int(F * 0.15), 1, 0, True, SEED, 1, None), 4 * L * F + 8 * NG * F),
+        # layer-wide fraction with max scores (the reference model's layer class): the weights are read twice
+        # (scores pass + rewire pass) and written once, the scores are written and read twice by the select block
+        ("rewire layer-wide fraction 0.15, max score, unused regrow, zero init, regroup",
+         lambda: hffi.rewire_ex(w2, loc, None, D, G, 0, 1, 2, 0.0, int(NG * F * 0.15), 1, 0, True, SEED, 1, None, rw_scratch), 6 * L * F + 8 * NG * F + 12 * NG * F),
     ]
     for name, fn, nbytes in rows:
         ms = timeit(fn)

@@ -242,8 +242,27 @@ int haste_ffi_rewire(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t F, 
     return fail(HASTE_ERR_BAD_ARG, "%s: bad mode", who);
   if (n_prune < 0 || n_prune > F) return fail(HASTE_ERR_BAD_ARG, "%s: n_prune=%d outside [0,F]", who, n_prune);
   if (regrow_mode == 1 && D < 2 * F) return fail(HASTE_ERR_UNSUPPORTED, "%s: 'unused' regrow needs D >= 2*F", who);
-  return launch_rewire(w, loc, mom_w, D, F, L, G, group0, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step,
-                       changed, static_cast<cudaStream_t>(stream));
+  return launch_rewire(w, loc, mom_w, D, F, L, G, group0, 0, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step,
+                       nullptr, changed, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int32_t score_mode,
+                        int32_t prune_mode, float threshold, int64_t n_prune, int32_t regrow_mode, int32_t init_mode, int32_t regroup,
+                        uint64_t seed, uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire_ex";
+  REQUIRE_PTR(w, who); REQUIRE_PTR(loc, who); REQUIRE_ALIGNED(w, who);
+  if (int rc = validate_shape(who, 1, D, F, L, G)) return rc;
+  if (score_mode < 0 || score_mode > 1 || prune_mode < 0 || prune_mode > 2 || regrow_mode < 0 || regrow_mode > 1 || init_mode < 0 || init_mode > 1)
+    return fail(HASTE_ERR_BAD_ARG, "%s: bad mode", who);
+  const int64_t NG = (L + G - 1) / G;
+  if (prune_mode == 1 && (n_prune < 0 || n_prune > F)) return fail(HASTE_ERR_BAD_ARG, "%s: n_prune=%lld outside [0,F]", who, (long long)n_prune);
+  if (prune_mode == 2) {
+    if (n_prune < 1 || n_prune > NG * F) return fail(HASTE_ERR_BAD_ARG, "%s: n_prune=%lld outside [1,NG*F]", who, (long long)n_prune);
+    REQUIRE_PTR(scratch, who); REQUIRE_ALIGNED(scratch, who);
+  }
+  if (regrow_mode == 1 && D < 2 * F) return fail(HASTE_ERR_UNSUPPORTED, "%s: 'unused' regrow needs D >= 2*F", who);
+  return launch_rewire(w, loc, mom_w, D, F, L, G, group0, score_mode, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed,
+                       step, scratch, changed, static_cast<cudaStream_t>(stream));
 }
 
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream) {

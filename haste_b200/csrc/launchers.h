@@ -61,8 +61,10 @@ int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, con
                           int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st);
 int launch_pad_rows(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols, cudaStream_t st);
 int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st);
-int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int prune_mode,
-                  float threshold, int n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,
-                  int32_t* changed, cudaStream_t st);
+// score_mode 0 mean / 1 max; prune_mode 0 threshold / 1 per-group fraction / 2 global fraction (n_prune is then the
+// layer-wide count and scratch holds HASTE_REWIRE_SCRATCH_WORDS(NG, F) words)
+int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int score_mode, int prune_mode,
+                  float threshold, int64_t n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,
+                  void* scratch, int32_t* changed, cudaStream_t st);
 
 }  // namespace haste

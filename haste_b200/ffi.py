@@ -209,6 +209,25 @@ def rewire(w, loc, mom_w, D, G, group0, prune_mode, threshold, n_prune, regrow_m
                                    regrow_mode, init_mode, int(bool(regroup)), seed, step, _ptr(changed), _stream(w)), "ffi_rewire")
 
 
+def rewire_scratch_words(NG, F):
+    """32-bit words of device scratch for layer-wide fraction pruning (HASTE_REWIRE_SCRATCH_WORDS)."""
+    return NG * F + NG + 2 + 2 * 65536 + 4
+
+
+def rewire_ex(w, loc, mom_w, D, G, group0, score_mode, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step,
+              changed=None, scratch=None):
+    """Rewire with 'mean'/'max' scores (0/1) and threshold / per-group fraction / layer-wide fraction pruning (0/1/2)."""
+    _req(w, "weights", torch.bfloat16); _req(loc, "group_locations", torch.int32)
+    L, F = w.shape
+    NG = (L + G - 1) // G
+    if prune_mode == 2 and scratch is None:
+        scratch = torch.empty(rewire_scratch_words(NG, F), dtype=torch.int32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(lib.haste_ffi_rewire_ex(_ptr(w), _ptr(loc), _ptr(mom_w), D, F, L, G, group0, score_mode, prune_mode, float(threshold), int(n_prune),
+                                      regrow_mode, init_mode, int(bool(regroup)), seed, step, _ptr(scratch), _ptr(changed), _stream(w)),
+              "ffi_rewire_ex")
+
+
 def check_locations(loc, D):
     _req(loc, "group_locations", torch.int32)
     with torch.cuda.device(loc.device):

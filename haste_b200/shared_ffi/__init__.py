@@ -47,4 +47,4 @@ def backward_weights(features, weights, locations, grad_outputs, gsize=32):
 from . import bindings, ops, sr_triton, optim_sr, rewire  # noqa: E402,F401
 from .ops import group_ffi_mul  # noqa: E402,F401
 from .optim_sr import SRSgd  # noqa: E402,F401
-from .rewire import GroupFixedFanIn  # noqa: E402,F401
+from .rewire import GroupFixedFanIn, GroupFixedFanInReal  # noqa: E402,F401

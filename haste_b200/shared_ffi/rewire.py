@@ -11,6 +11,8 @@ GROWTH_MODES = ['random']
 PRUNE_MODES = ['threshold', 'fraction']
 INIT_MODES = ["random", "zero"]
 REGROW_MODES = ["replace", "unused"]
+SCORE_MODES = ["mean", "max"]
+PRUNE_SCOPES = ["group", "global"]
 
 
 class GroupFixedFanIn(torch.nn.Module):
@@ -19,13 +21,16 @@ class GroupFixedFanIn(torch.nn.Module):
 
     Constructor arguments are the reference's.  Keyword-only additions: ``regrow`` ('replace' = uniform with
     replacement as in the reference; 'unused' = only indices the row does not hold yet), ``regroup`` (sort
-    every index row after rewiring and permute the weight columns with it) and ``seed`` for the Philox draws.
+    every index row after rewiring and permute the weight columns with it), ``seed`` for the Philox draws,
+    ``score_mode`` ('mean' or 'max' of |w| over a group's rows) and ``prune_scope`` ('group': the fraction is
+    taken inside every group, as shared_ffi/rewire.py does; 'global': over all (group, slot) pairs of the layer,
+    as src/group_fanin_real.py:232-250 does).
     """
     __constants__ = ['in_features', 'out_features', 'fan_in']
 
     def __init__(self, in_features: int, out_features: int, fan_in: int, bias: bool = True, device=None, dtype=None, *,
                  group_size=32, prune_mode="threshold", rewire_threshold=None, rewire_fraction=None, growth_mode="random",
-                 init_mode="random", regrow="replace", regroup=False, seed=0, **kwargs):
+                 init_mode="random", regrow="replace", regroup=False, seed=0, score_mode="mean", prune_scope="group", **kwargs):
         super().__init__(**kwargs)
         factory_kwargs = {'device': device, 'dtype': dtype}
         self.in_features, self.out_features, self.fan_in = in_features, out_features, fan_in
@@ -33,12 +38,15 @@ class GroupFixedFanIn(torch.nn.Module):
         assert growth_mode in GROWTH_MODES, f"Invalid growth_mode={growth_mode}; supported: {GROWTH_MODES}"
         assert init_mode in INIT_MODES, f"Invalid init_mode={init_mode}; supported: {INIT_MODES}"
         assert regrow in REGROW_MODES, f"Invalid regrow={regrow}; supported: {REGROW_MODES}"
+        assert score_mode in SCORE_MODES, f"Invalid score_mode={score_mode}; supported: {SCORE_MODES}"
+        assert prune_scope in PRUNE_SCOPES, f"Invalid prune_scope={prune_scope}; supported: {PRUNE_SCOPES}"
         if prune_mode == "threshold" and rewire_threshold is None:
             raise ValueError("rewire_threshold must be specified for prune_mode 'threshold'")
         elif prune_mode == "fraction" and rewire_fraction is None:
             raise ValueError("rewire_fraction must be specified for prune_mode 'fraction'")
         self.prune_mode, self.growth_mode, self.init_mode = prune_mode, growth_mode, init_mode
         self.regrow, self.regroup, self.seed = regrow, bool(regroup), int(seed)
+        self.score_mode, self.prune_scope = score_mode, prune_scope
         self._rewire_calls = 0
         if prune_mode == 'fraction':
             self.rewire_fraction = rewire_fraction
@@ -78,15 +86,32 @@ class GroupFixedFanIn(torch.nn.Module):
         if self.out_features == 0:
             return 0
         if self.prune_mode == 'fraction':
-            n_prune = int(self.fan_in * self.rewire_fraction)
+            if self.prune_scope == 'global':
+                n_prune, mode = int(self.num_groups * self.fan_in * self.rewire_fraction), 2
+            else:
+                n_prune, mode = int(self.fan_in * self.rewire_fraction), 1
             if n_prune == 0:
                 return 0
-            mode, thr = 1, 0.0
+            thr = 0.0
         else:
             n_prune, mode, thr = 0, 0, float(self.rewire_threshold)
         changed = torch.zeros(1, dtype=torch.int32, device=self.weights.device)
-        _ffi.rewire(self.weights.data, self.group_locations, momentum_buf, self.in_features, self.group_size, 0, mode, thr,
-                    n_prune, {'replace': 0, 'unused': 1}[self.regrow], {'zero': 0, 'random': 1}[self.init_mode], self.regroup, self.seed,
-                    self._rewire_calls, changed)
+        _ffi.rewire_ex(self.weights.data, self.group_locations, momentum_buf, self.in_features, self.group_size, 0,
+                       SCORE_MODES.index(self.score_mode), mode, thr, n_prune, {'replace': 0, 'unused': 1}[self.regrow],
+                       {'zero': 0, 'random': 1}[self.init_mode], self.regroup, self.seed, self._rewire_calls, changed)
         self._rewire_calls += 1
         return int(changed.item())
+
+
+class GroupFixedFanInReal(GroupFixedFanIn):
+    """The layer class the reference's model builds (src/group_fanin_real.py:34-286, src/model.py:188-204): same
+    parameters and forward as ``GroupFixedFanIn``; ``rewire`` scores slots by the 'mean' or 'max' of |w| and, in
+    'fraction' mode, prunes the lowest ``int(num_groups * fan_in * rewire_fraction)`` slots of the whole layer."""
+
+    def __init__(self, in_features: int, out_features: int, fan_in: int, bias: bool = True, device=None, dtype=None, *,
+                 group_size=32, prune_mode="threshold", rewire_threshold=None, rewire_fraction=None, growth_mode="random",
+                 init_mode="random", score_mode="mean", **kwargs):
+        super().__init__(in_features, out_features, fan_in, bias, device, dtype, group_size=group_size, prune_mode=prune_mode,
+                         rewire_threshold=rewire_threshold, rewire_fraction=rewire_fraction, growth_mode=growth_mode,
+                         init_mode=init_mode, score_mode=score_mode, prune_scope="global", **kwargs)
+        self.use_grad = False

@@ -202,6 +202,22 @@ int haste_ffi_rewire(void* w, int32_t* loc, float* mom_w,
                      int32_t regrow_mode, int32_t init_mode, int32_t regroup,
                      uint64_t seed, uint32_t step, int32_t* changed, haste_stream_t stream);
 
+/* Rewire with the scoring and pruning rules of the layer class the reference's model instantiates
+ * (GroupFixedFanInReal.rewire, src/group_fanin_real.py:149-286):
+ *   score_mode 0 'mean' (as above), 1 'max': score[g,k] = max over the group's real rows of |w[l,k]|
+ *   prune_mode 0 'threshold', 1 'fraction' per group (n_prune slots of every group, as haste_ffi_rewire),
+ *              2 'fraction' over the whole layer: the n_prune = int(NG*F*fraction) lowest scores of all
+ *                (group, slot) pairs (src/group_fanin_real.py:232-250); ties at the n_prune-th score go to the
+ *                lowest flat (group, slot) index (the reference leaves them to torch.topk).
+ * scratch (prune_mode 2 only, 16-byte aligned device memory): HASTE_REWIRE_SCRATCH_WORDS(NG, F) * 4 bytes.
+ * Everything else as haste_ffi_rewire.  With a sharded layer "the whole layer" is this shard. */
+#define HASTE_REWIRE_SCRATCH_WORDS(NG, F) ((int64_t)(NG) * (F) + (NG) + 2 + 2 * 65536 + 4)
+int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w,
+                        int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0,
+                        int32_t score_mode, int32_t prune_mode, float threshold, int64_t n_prune,
+                        int32_t regrow_mode, int32_t init_mode, int32_t regroup,
+                        uint64_t seed, uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream);
+
 /* Debug check: every loc value in [0,D).  Synchronises the stream. */
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream);
 

@@ -134,3 +134,20 @@ def test_fused_shard_matches_two_half_shards(sf):
     assert torch.equal(torch.cat(ws), full.w)
     assert torch.allclose(dsum, dxt_full, rtol=1e-4, atol=1e-4 * float(dxt_full.abs().max()))
     assert abs(lsum - loss_full) <= 1e-4 * abs(loss_full)
+
+
+def test_layer_real_global_rewire(sf):
+    """``GroupFixedFanInReal`` (the class src/model.py builds): layer-wide fraction pruning with max scores."""
+    D, L, F, G = 256, 128 * 9 + 5, 64, 128
+    layer = sf.GroupFixedFanInReal(D, L, F, bias=True, device="cuda", dtype=torch.bfloat16, group_size=G, prune_mode="fraction",
+                                   rewire_fraction=0.2, init_mode="zero", score_mode="max", regrow="replace", seed=9)
+    W0, loc0 = layer.weights.detach().cpu().clone(), layer.group_locations.cpu().clone()
+    n = layer.rewire()
+    NG = loc0.shape[0]
+    assert n == int(NG * F * 0.2)
+    W1, loc1, _ = fo.rewire(W0, loc0, G, D, "fraction", 0.2, None, init_mode="zero", regrow="replace", regroup=False, seed=9, step=0,
+                            score_mode="max", prune_scope="global")
+    assert np.array_equal(layer.group_locations.cpu().numpy(), loc1.numpy())
+    assert np.array_equal(fo._bf16_to_bits(layer.weights.detach().cpu()), fo._bf16_to_bits(W1))
+    x = torch.randn(4, D, device="cuda", dtype=torch.bfloat16)
+    assert layer(x).shape == (4, L)
