@@ -101,6 +101,59 @@ def test_split_groups_by_cost():
     assert torch.all(group_cost_from_targets(torch.zeros(0, 2, dtype=torch.int32), L, G, B) == 1.0)
 
 
+def test_checkpoint_interop(tmp_path):
+    """Reference-style state dict -> shards (count split and cost split) -> merged state dict is the identity;
+    group-row inflation follows src/runner.py:324-334; the optimizer state keeps its rounding seed."""
+    import torch
+    from haste_b200 import checkpoint as ck
+    from haste_b200.fused import FusedFFIShard
+    gen = torch.Generator().manual_seed(2)
+    D, L, F, G = 64, 128 * 5 + 17, 64, 128
+    NG = (L + G - 1) // G
+    sd = {"encoder.x": torch.zeros(3),
+          "tail_layer.weights": torch.randn(L, F, generator=gen).to(torch.bfloat16),
+          "tail_layer.bias": torch.randn(L, generator=gen).to(torch.bfloat16),
+          "tail_layer.group_locations": torch.randint(0, D, (NG, F), generator=gen, dtype=torch.int32)}
+    path = tmp_path / "ckpt.pt"
+    torch.save({"state_dict": sd, "epoch": 3}, path)
+    sd2 = torch.load(path)["state_dict"]
+    inflated = ck.inflate_group_locations(sd2["tail_layer.group_locations"], L, G)
+    assert inflated.shape == (L, F)
+    for l in (0, G - 1, G, L - 1):
+        assert torch.equal(inflated[l], sd["tail_layer.group_locations"][l // G])
+    cost = torch.ones(NG, dtype=torch.float64)
+    cost[0] = 3.0
+    for gc in (None, cost):
+        world = 3
+        shards = [ck.shard_from_state_dict(sd2, "tail_layer.", G, D, r, world, "cpu", group_cost=gc, loss="bce", momentum=0.9, seed=77)
+                  for r in range(world)]
+        assert sum(s.L for s in shards) == L and shards[0].label0 == 0
+        for i, s in enumerate(shards):
+            s.steps = 5 + i
+            s.mom_w.fill_(0.25)
+        states = [ck.shard_state(s) for s in reversed(shards)]                 # any order
+        merged = ck.merge_shard_states(states, prefix="tail_layer.")
+        for k in ("weights", "bias", "group_locations"):
+            assert torch.equal(merged["tail_layer." + k], sd["tail_layer." + k]), k
+        # a fresh shard of the same range resumes with the same random-stream position and momentum
+        fresh = ck.shard_from_state_dict(sd2, "tail_layer.", G, D, 1, world, "cpu", group_cost=gc, loss="bce", momentum=0.9, seed=1)
+        fresh.w.zero_()
+        ck.load_shard_state(fresh, [st for st in states if st["label0"] == fresh.label0][0])
+        assert fresh.steps == 6 and fresh.seed == 77 and torch.equal(fresh.w, shards[1].w) and float(fresh.mom_w[0, 0]) == 0.25
+        assert fresh._keys() == shards[1]._keys()
+    with pytest.raises(ValueError):
+        ck.merge_shard_states(states[:-1])                                     # the first shard is missing
+    # SRSgd keeps seed and step counter in its param group, so optimizer.state_dict() round-trips them
+    from haste_b200.shared_ffi.optim_sr import SRSgd
+    p = torch.nn.Parameter(torch.zeros(4, 16, dtype=torch.bfloat16))
+    opt = SRSgd([p], lr=0.1, seed=123, rng="packed")
+    opt.param_groups[0]["seed"] += 7
+    opt.param_groups[0]["step_count"] = 7
+    opt2 = SRSgd([p], lr=0.1, seed=0)
+    opt2.load_state_dict(opt.state_dict())
+    assert opt2.param_groups[0]["seed"] == 130 and opt2.param_groups[0]["step_count"] == 7 and opt2.param_groups[0]["rng"] == "packed"
+
+
 _WORKER = r"""
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
