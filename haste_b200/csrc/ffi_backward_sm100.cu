@@ -9,7 +9,7 @@
 // (dY slice, now copied in by the producers instead of computed by an epilogue), the X tile and the W tile sit
 // in 128-byte-swizzled shared memory; backward-features takes Y as K-major A and W as MN-major B,
 // backward-weights takes Y as MN-major A and X as K-major B.  Warp roles (512 threads): warps 0 and 2 producers
-// (cp.async; items W | X(t) | Y(t) dealt round-robin), warp 1 issues backward-features, warp 3 backward-weights,
+// (cp.async; one producer warp per ring stage), warp 1 issues backward-features, warp 3 backward-weights,
 // warps 4-11 drain dXg (TMEM -> registers -> coalesced red.global.add.f32), warps 12-15 turn the dW accumulator
 // into bf16 rows of dw / dbias at the end of each group.  Requires 16-byte-aligned dY rows (ldy % 8 == 0).
 #include "common.cuh"
@@ -40,7 +40,8 @@ constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_YFULL = 2 * NXS, B_YEMPTY = B_YFULL
               B_DWEMPTY = B_DWFULL + 2, B_LEMPTY = B_DWEMPTY + 2, NBAR = B_LEMPTY + 2;
 static_assert(NBAR <= 40, "barrier space");
 constexpr int N_EB = 8, N_EC = 4;
-constexpr int NTHREADS = (4 + N_EB + N_EC) * 32;
+constexpr int N_XPROD = 5;                    // producer warps beyond the two among the first four warps
+constexpr int NTHREADS = (4 + N_EB + N_EC + N_XPROD) * 32;
 constexpr uint32_t TM_DX = 0, TM_DW = 128, TM_DW_STRIDE = 80, TM_COLS = 512;
 constexpr long long WAIT_LIMIT = 4000000000ll;
 
@@ -102,10 +103,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
   const uint32_t tmem = *tmem_slot;
   const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
 
-  if (warp == 0 || warp == 2) {
+  if (warp == 0 || warp == 2 || warp >= 4 + N_EB + N_EC) {
     // ================================================================ producers
-    const int p = warp >> 1;
-    int item = 0, it = 0;
+    // Each producer warp has one item in flight at a time and pays the full memory latency for it (dY tiles come
+    // from HBM), so the load rate is the number of producer warps over that latency.  Every ring stage has its
+    // own producer warp — NYS warps for the dY ring, NXS for the X ring, the first X warp also loads the W tiles —
+    // so one warp sees all phases of its stage's barriers in order (a producer dealt arbitrary items could run a
+    // full ring ahead of a slower one and mistake an old phase of the one-bit parity for the one it waits for).
+    static_assert(2 + N_XPROD == NXS + NYS, "one producer warp per ring stage");
+    const int p = warp < 4 ? (warp >> 1) : 2 + warp - (4 + N_EB + N_EC);
+    const bool y_prod = p < NYS;
+    const int my_stage = y_prod ? p : p - NYS;
+    const bool w_prod = p == NYS;
+    int it = 0;
     auto land = [&](uint32_t full_bar) {
       cp_async_commit();
       cp_async_wait<0>();
@@ -121,7 +131,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
       const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
       const int loc_lo = min(max(__ldg(lrow + lane), 0), a.D - 1);
       const int loc_hi = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
-      if ((item & 1) == p) {
+      if (w_prod) {
         mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WAIT_LIMIT, 100);
         mbar_wait(bar(B_LEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WAIT_LIMIT, 100);
         __syncwarp();
@@ -135,10 +145,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
         }
         land(bar(B_WFULL + ws));
       }
-      ++item;
       for (int t = 0; t < T; ++t, ++it) {
         const int64_t b0 = static_cast<int64_t>(t) * BT;
-        if ((item & 1) == p) {            // ---- X item
+        if (!y_prod && it % NXS == my_stage) {            // ---- X item
           const int xs = it % NXS;
           mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 32, WAIT_LIMIT, 100);
           __syncwarp();
@@ -155,8 +164,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
           }
           land(bar(B_XFULL + xs));
         }
-        ++item;
-        if ((item & 1) == p) {            // ---- Y item: dy[b0 .. b0+127, l0 .. l0+127] -> two 64-label blocks
+        if (y_prod && it % NYS == my_stage) {            // ---- Y item: dy[b0 .. b0+127, l0 .. l0+127] -> two 64-label blocks
           const int ys = it % NYS;
           mbar_wait(bar(B_YEMPTY + ys), ((it / NYS) & 1) ^ 1, abort_flag, a.err, 33, WAIT_LIMIT, 100);
           __syncwarp();
@@ -174,7 +182,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
           }
           land(bar(B_YFULL + ys));
         }
-        ++item;
       }
     }
   } else if (warp == 1 || warp == 3) {
@@ -280,7 +287,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_LEMPTY + ws));
     }
-  } else if (warp >= 4 + N_EB) {
+  } else if (warp >= 4 + N_EB && warp < 4 + N_EB + N_EC) {
     // ================================================================ dW / dbias rows out of the accumulator
     const int q = warp & 3;
     const int row = q * 32 + lane;                  // label row inside the group == TMEM lane

@@ -35,7 +35,9 @@ constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_WFULL = 2 * NXS, B_WEMPTY = B_WFULL
               B_ZEMPTY = B_ZFULL + 2, B_BEMPTY = B_ZEMPTY + 2, NBAR = B_BEMPTY + 2;
 static_assert(NBAR <= 32, "barrier space");
 constexpr int N_EPI = 8;                      // epilogue warps: 4 TMEM lane quarters x 2 column halves
-constexpr int NTHREADS = (4 + N_EPI) * 32;
+constexpr int N_SETS = 2;                     // sets of epilogue warps; set s takes the tiles whose Z stage (and staging buffer) is s
+constexpr int N_XPROD = 1;                    // producer warps beyond the three among the first four warps
+constexpr int NTHREADS = (4 + N_EPI * N_SETS + N_XPROD) * 32;
 constexpr uint32_t TM_COLS = 256;             // two 128-column accumulator stages
 constexpr long long WAIT_LIMIT = 4000000000ll;
 
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
       mbar_init(bar(B_ZFULL + i), 1);  mbar_init(bar(B_ZEMPTY + i), N_EPI);
-      mbar_init(bar(B_BEMPTY + i), N_EPI);     // the epilogue warps are done with the group's bias row
+      mbar_init(bar(B_BEMPTY + i), N_EPI * N_SETS);     // the epilogue warps are done with the group's bias row
     }
     mbar_fence_init();
     *abort_flag = 0;
@@ -86,10 +88,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
   const uint32_t tmem = *tmem_slot;
   const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
 
-  if (warp == 0 || warp == 2) {
-    // ================================================================ producers (items dealt round-robin)
-    const int p = warp >> 1;
-    int item = 0, it = 0;
+  if (warp == 0 || warp == 2 || warp == 3 || warp >= 4 + N_EPI * N_SETS) {
+    // ================================================================ producers
+    // Each producer warp has one item (a W tile or an X tile) in flight at a time and pays the full memory latency
+    // for it, so the gather rate is the number of producer warps over that latency: 3 + N_XPROD warps.  X tiles
+    // are dealt by tile index and the warp count divides the ring depth, so every ring stage is always filled by
+    // the same warp, which therefore sees all phases of that stage's barriers in order; the last producer warp
+    // loads the W tiles and nothing else.
+    constexpr int N_PROD = 3 + N_XPROD - 1;           // X producers
+    static_assert(N_XPROD >= 1 && NXS % N_PROD == 0, "every X stage belongs to one producer warp");
+    const int p = warp == 0 ? 0 : (warp < 4 ? warp - 1 : 3 + warp - (4 + N_EPI * N_SETS));
+    int it = 0;
     auto land = [&](uint32_t full_bar) {
       cp_async_commit();
       cp_async_wait<0>();
@@ -105,7 +114,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
       const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
       const int loc_lo = min(max(__ldg(lrow + lane), 0), a.D - 1);
       const int loc_hi = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
-      if ((item & 1) == p) {
+      if (p == N_PROD) {
         mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 21, WAIT_LIMIT, 100);
         mbar_wait(bar(B_BEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 21, WAIT_LIMIT, 100);
         __syncwarp();
@@ -122,9 +131,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
         }
         land(bar(B_WFULL + ws));
       }
-      ++item;
-      for (int t = 0; t < T; ++t, ++it, ++item) {
-        if ((item & 1) != p) continue;
+      for (int t = 0; t < T; ++t, ++it) {
+        if (p == N_PROD || (it % N_PROD) != p) continue;
         const int xs = it % NXS;
         mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 22, WAIT_LIMIT, 100);
         __syncwarp();
@@ -179,11 +187,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 4 + N_EPI * N_SETS) {
     // ================================================================ epilogue
-    const int ep = warp - 4, q = ep & 3, h = ep >> 2;        // TMEM lane quarter, column half (64 labels)
+    // Two sets of eight warps take alternate tiles: while one set drains its staging tile to global memory, the
+    // other reads the next accumulator stage, so neither the TMEM reads nor the stores wait for each other.
+    const int ep = warp - 4, set = ep / N_EPI, es = ep % N_EPI;
+    const int q = es & 3, h = es >> 2;                       // TMEM lane quarter, column half (64 labels)
     const int row = q * 32 + lane;
-    const int et = tid - 128;                                // 0..255
+    const int et = tid - 128 - set * N_EPI * 32;             // 0..255 inside the set
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = blockIdx.x + gi * gridDim.x;
@@ -193,6 +204,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 26, WAIT_LIMIT);    // bias row in place
       const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + h * 64);
       for (int t = 0; t < T; ++t, ++it) {
+        if (N_SETS > 1 && (it & 1) != set) continue;         // the other set's tile
         const int zs = it & 1;
         const int64_t b0 = static_cast<int64_t>(t) * BT;
         mbar_wait(bar(B_ZFULL + zs), (it >> 1) & 1, abort_flag, a.err, 27, WAIT_LIMIT);
@@ -221,7 +233,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_ZEMPTY + zs));
-        named_bar_sync(1, N_EPI * 32);               // the whole staging tile is written
+        named_bar_sync(1 + set, N_EPI * 32);         // the set's whole staging tile is written
         // coalesced store: 16 lanes cover one 256-byte row segment; 8 KB per pass of the 256 threads
         const uint8_t* cbase = sm + OFF_C + zs * CSTAGE;
         if (!*abort_flag) {
@@ -240,8 +252,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
             }
           }
         }
-        // the staging buffer of this parity is rewritten two tiles later; every thread passes the next tile's
-        // barrier only after its stores above, so no second barrier is needed
+        // the set's next tile reuses this staging buffer: nobody may write it before everybody has read it
+        named_bar_sync(1 + set, N_EPI * 32);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_BEMPTY + ws));
