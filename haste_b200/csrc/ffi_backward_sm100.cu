@@ -8,10 +8,10 @@
 // Persistent, one CTA per SM.  Same operand layouts as the fused train step: per 128-row batch tile the Y tile
 // (dY slice, now copied in by the producers instead of computed by an epilogue), the X tile and the W tile sit
 // in 128-byte-swizzled shared memory; backward-features takes Y as K-major A and W as MN-major B,
-// backward-weights takes Y as MN-major A and X as K-major B.  Warp roles (512 threads): warps 0 and 2 producers
-// (cp.async; one producer warp per ring stage), warp 1 issues backward-features, warp 3 backward-weights,
-// warps 4-11 drain dXg (TMEM -> registers -> coalesced red.global.add.f32), warps 12-15 turn the dW accumulator
-// into bf16 rows of dw / dbias at the end of each group.  Requires 16-byte-aligned dY rows (ldy % 8 == 0).
+// backward-weights takes Y as MN-major A and X as K-major B.  Warp roles (672 threads): warps 0, 2 and 16-20 are
+// producers (cp.async; one producer warp per ring stage), warp 1 issues backward-features, warp 3
+// backward-weights, warps 4-11 drain dXg (TMEM -> registers -> coalesced red.global.add.f32), warps 12-15 turn
+// the dW accumulator into bf16 rows of dw / dbias at the end of each group.  Requires 16-byte-aligned dY rows (ldy % 8 == 0).
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100.cuh"
