@@ -353,7 +353,10 @@ def run_aux(args):
     mom = torch.zeros(L, F, device=dev)
     w2 = W.clone()
     rw_scratch = torch.empty(hffi.rewire_scratch_words(NG, F), dtype=torch.int32, device=dev)
+    fill_buf = torch.empty(768 << 20, dtype=torch.uint8, device=dev)
     rows = [
+        # what a write-only stream reaches on this GPU (a library fill): the yardstick for the forward, which writes [B,L]
+        ("device fill 768 MiB (write-only yardstick, torch fill kernel)", lambda: fill_buf.zero_(), 768 << 20),
         ("ffi_forward (unfused, writes Z)", lambda: hffi.forward(loc, xt, W, bias, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_features (unfused, reads dY)", lambda: hffi.backward_features(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_weights (unfused, reads dY, writes dW)", lambda: hffi.backward_weights(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
