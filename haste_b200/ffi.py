@@ -161,6 +161,18 @@ def train_step(loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, l
                                        mu, seed, step, flags, _stream(xt)), "ffi_train_step")
 
 
+def step(x, coo, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, mu, seed, step_no,
+         flags):
+    """Preparation + fused step in one library call (the per-step path of ``FusedFFIShard.step``: argument checks are
+    the caller's, done once when the buffers are created)."""
+    B, D = x.shape
+    L, F = w.shape
+    with torch.cuda.device(x.device):
+        check(lib.haste_ffi_step(_ptr(x), _ptr(coo), coo.shape[0], _ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), _ptr(mom_w), _ptr(mom_b),
+                                 _ptr(tgt_ptr), _ptr(tgt_ent), _ptr(dxt), _ptr(loss), B, D, F, L, G, label0, loss_kind, grad_scale, lr, wd,
+                                 mu, seed, step_no, flags, _stream(x)), "ffi_step")
+
+
 def train_step_dbg(loc, xt, w, bias, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, seed, step, flags):
     """The fused step with debug outputs: returns (z bf16 [B,L], dw bf16 [L,F], dbias bf16 [L])."""
     _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)

@@ -151,12 +151,14 @@ class FusedFFIShard:
             self._xt = torch.empty(D, B, dtype=torch.bfloat16, device=x.device)
         if targets.shape[0] > self.tgt_ent.numel():
             self.tgt_ent = torch.zeros(int(targets.shape[0] * 1.5) + 1, dtype=torch.int32, device=targets.device)
-        _ffi.step_prepare(x, self._xt, self._dxt, self.loss_buf, targets, self.label0, self.L, self.G, self.tgt_ptr, self.tgt_ent)
+        if not (x.is_cuda and targets.is_cuda) or x.dtype != torch.bfloat16 or targets.dtype != torch.int32 or not x.is_contiguous() \
+                or not targets.is_contiguous():
+            raise RuntimeError("FusedFFIShard.step: features must be a contiguous CUDA bf16 [B,D] tensor, targets a contiguous CUDA int32 [nnz,2] tensor")
         seed, step = self._keys()
         flags = _ffi.make_flags(sr=self.sr, contract=self.contract, rng=self.rng, zero_dxt=False, loss=want_loss)
-        _ffi.train_step(self.loc, self._xt, self.w, self.bias, self.mom_w, self.mom_b, self.tgt_ptr, self.tgt_ent, self._dxt,
-                        self.loss_buf if want_loss else None, self.G, self.label0, self.loss_kind, self.grad_scale, self.lr,
-                        self.wd, self.mu, seed, step, flags)
+        # the loss word is cleared by the preparation launch either way; it is only accumulated when asked for
+        _ffi.step(x, targets, self.loc, self._xt, self.w, self.bias, self.mom_w, self.mom_b, self.tgt_ptr, self.tgt_ent, self._dxt,
+                  self.loss_buf, self.G, self.label0, self.loss_kind, self.grad_scale, self.lr, self.wd, self.mu, seed, step, flags)
         self.steps += 1
         return self._dxt, (self.loss_buf if want_loss else None)
 

@@ -218,6 +218,17 @@ int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w,
                         int32_t regrow_mode, int32_t init_mode, int32_t regroup,
                         uint64_t seed, uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream);
 
+/* One training step from the batch as the data loader delivers it: haste_ffi_step_prepare followed by
+ * haste_ffi_train_step in one call (two launches, one crossing of the language boundary).  x bf16 [B,D]; coo int32
+ * [nnz,2]; xt, dxt, tgt_ptr, tgt_ent are work buffers the caller keeps between steps (sizes as in the two
+ * functions); HASTE_F_ZERO_DXT is implied.  Replaces forward + loss + backward + optimizer step of
+ * src/runner.py:205-230 for the FFI layer. */
+int haste_ffi_step(const void* x, const int32_t* coo, int64_t nnz, const int32_t* loc, void* xt, void* w, void* bias,
+                   float* mom_w, float* mom_b, int32_t* tgt_ptr, uint32_t* tgt_ent, float* dxt, float* loss,
+                   int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t label0, int32_t loss_kind,
+                   float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step, uint32_t flags,
+                   haste_stream_t stream);
+
 /* Debug check: every loc value in [0,D).  Synchronises the stream. */
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream);
 
