@@ -37,7 +37,7 @@ LR, WD, SEED = 0.05, 1e-4, 123
 N_BATCHES = 4
 # dram bytes (read+write) of one fused-step launch from an ncu capture; filled per workload when a capture exists
 # (see profiles/); None = not captured yet.
-NCU_TRAFFIC_BYTES = {"c3": 126.7e6}   # profiles/train_step_sm100_c3.md: dram read 90.9 MB + write 35.8 MB
+NCU_TRAFFIC_BYTES = {"c3": 126.7e6}   # ncu capture of one launch at C3: dram read 90.9 MB + write 35.8 MB
 
 
 def measured_peaks():
