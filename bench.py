@@ -354,6 +354,8 @@ def run_aux(args):
     w2 = W.clone()
     rw_scratch = torch.empty(hffi.rewire_scratch_words(NG, F), dtype=torch.int32, device=dev)
     fill_buf = torch.empty(768 << 20, dtype=torch.uint8, device=dev)
+    from haste_b200.infer import ffi_topk
+    x_bd = xt.t().contiguous()
     rows = [
         # what a write-only stream reaches on this GPU (a library fill): the yardstick for the forward, which writes [B,L]
         ("device fill 768 MiB (write-only yardstick, torch fill kernel)", lambda: fill_buf.zero_(), 768 << 20),
@@ -365,6 +367,10 @@ def run_aux(args):
         ("sgd_sr_update packed stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 6 * L * F),
         ("sgd_sr_update reference stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="reference")), 6 * L * F),
         ("sgd_sr_update packed + momentum", lambda: hffi.sgd_sr_update(w2, g, mom, 0, LR, WD, 0.9, SEED, 1, hffi.make_flags(rng="packed")), 14 * L * F),
+        # inference top-100 (what the reference's evaluation does with torch.topk over the full logits): chunked forward +
+        # running top-k, [B,L] never written; bytes = the layer read once + the result
+        ("ffi_topk k=100 (chunked forward + running top-k, no [B,L] in HBM)", lambda: ffi_topk(loc, W, bias, x_bd, 100, G), 2 * L * F + 4 * NG * F + 8 * B * 100),
+        ("forward + torch.topk k=100 (library top-k over the full [B,L] logits)", lambda: torch.topk(hffi.forward(loc, xt, W, bias, G), 100, dim=1), 4 * B * L + 2 * L * F + 4 * NG * F),
         ("rewire fraction 0.15, unused regrow, zero init, regroup", lambda: hffi.rewire(w2, loc, None, D, G, 0, 1, 0.0, int(F * 0.15), 1, 0, True, SEED, 1, None), 4 * L * F + 8 * NG * F),
         # layer-wide fraction with max scores (the reference model's layer class): the weights are read twice
         # (scores pass + rewire pass) and written once, the scores are written and read twice by the select block

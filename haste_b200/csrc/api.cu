@@ -274,6 +274,16 @@ int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t 
                        step, scratch, changed, static_cast<cudaStream_t>(stream));
 }
 
+int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int32_t k, float* vals, int32_t* idx,
+                      haste_stream_t stream) {
+  const char* who = "haste_topk_update";
+  if (B < 0 || C < 0 || ldz < C || col0 < 0) return fail(HASTE_ERR_BAD_ARG, "%s: bad sizes", who);
+  if (k < 1 || k > 128) return fail(HASTE_ERR_UNSUPPORTED, "%s: k=%d outside [1,128]", who, k);
+  if (col0 + C >= (1ll << 31)) return fail(HASTE_ERR_UNSUPPORTED, "%s: label ids must fit in int32", who);
+  if (B > 0 && C > 0) { REQUIRE_PTR(z, who); REQUIRE_PTR(vals, who); REQUIRE_PTR(idx, who); }
+  return launch_topk_update(z, ldz, B, C, col0, k, vals, idx, static_cast<cudaStream_t>(stream));
+}
+
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream) {
   const char* who = "haste_ffi_check_locations";
   REQUIRE_PTR(loc, who);

@@ -240,6 +240,16 @@ def rewire_ex(w, loc, mom_w, D, G, group0, score_mode, prune_mode, threshold, n_
               "ffi_rewire_ex")
 
 
+def topk_update(z, C, col0, vals, idx):
+    """Fold logits z[:, :C] (labels col0..col0+C-1) into the running top-k state (vals fp32 [B,k], idx int32 [B,k])."""
+    _req(z, "logits", torch.bfloat16, contiguous=False); _req(vals, "vals", torch.float32); _req(idx, "idx", torch.int32)
+    if z.dim() != 2 or z.stride(1) != 1:
+        raise RuntimeError("logits must be [B, C] with unit column stride")
+    B, k = vals.shape
+    with torch.cuda.device(z.device):
+        check(lib.haste_topk_update(_ptr(z), z.stride(0), B, C, col0, k, _ptr(vals), _ptr(idx), _stream(z)), "topk_update")
+
+
 def check_locations(loc, D):
     _req(loc, "group_locations", torch.int32)
     with torch.cuda.device(loc.device):

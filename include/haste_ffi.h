@@ -229,6 +229,14 @@ int haste_ffi_step(const void* x, const int32_t* coo, int64_t nnz, const int32_t
                    float grad_scale, float lr, float wd, float mu, uint64_t seed, uint32_t step, uint32_t flags,
                    haste_stream_t stream);
 
+/* Fold a chunk of logits into the running per-row top-k (inference; the reference materialises [B,L] logits and
+ * calls torch.topk(logits, 100) / topk(5), src/evaluate.py:151-156, 219).  z: bf16 [B, ldz], columns 0..C-1 hold
+ * the logits of labels col0 .. col0+C-1.  vals fp32 [B,k] (descending) and idx int32 [B,k] are the state: start
+ * them at -inf / -1 and feed the chunks in increasing label order; equal values keep the lower label id first.
+ * 1 <= k <= 128. */
+int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int32_t k,
+                      float* vals, int32_t* idx, haste_stream_t stream);
+
 /* Debug check: every loc value in [0,D).  Synchronises the stream. */
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream);
 

@@ -476,3 +476,42 @@ def test_step_prepare(hb):
         e0, e1 = ent0.cpu().numpy(), ent1.cpu().numpy()
         for g in np.nonzero(np.diff(p0))[0]:
             assert sorted(e0[p0[g]:p0[g + 1]]) == sorted(e1[p1[g]:p1[g + 1]])
+
+
+# ------------------------------------------------------------------------------------------------ inference top-k
+@pytest.mark.parametrize("cfg", [
+    dict(B=64, D=256, L=128 * 40 + 7, F=64, G=128, k=100, chunk=7),
+    dict(B=33, D=96, L=1000, F=32, G=32, k=5, chunk=4),
+    dict(B=16, D=128, L=300, F=16, G=64, k=128, chunk=2),
+    dict(B=8, D=64, L=50, F=16, G=16, k=100, chunk=None),          # fewer labels than k: the tail stays (-inf, -1)
+])
+def test_topk_chunked_matches_full(hb, cfg):
+    """Chunked forward + running top-k against torch.topk over the full logits of the same forward kernel.
+    Values must match exactly; label ids must match wherever the value is unique in its row, and must point at a
+    logit of that value everywhere (torch.topk leaves the order of equal values open; here it is by label id)."""
+    ffi, _ = hb
+    from haste_b200.infer import ffi_topk
+    B, D, L, F, G, k = cfg["B"], cfg["D"], cfg["L"], cfg["F"], cfg["G"], cfg["k"]
+    inp = fo.make_inputs(B, D, L, F, G, 2, 1.1, seed=29, x_kind="normal", bias_zero=False)
+    dev = {n: v.cuda() for n, v in inp.items()}
+    vals, idx = ffi_topk(dev["loc"], dev["W"], dev["bias"], dev["X"], k, G, groups_per_chunk=cfg["chunk"], label0=5)
+    z = ffi.forward(dev["loc"], dev["X"].t().contiguous(), dev["W"], dev["bias"], G).float()
+    kk = min(k, L)
+    want_v, want_i = torch.topk(z, kk, dim=1)
+    assert torch.equal(vals[:, :kk], want_v)
+    if kk < k:
+        assert torch.isinf(vals[:, kk:]).all() and (idx[:, kk:] == -1).all()
+    got_i = idx[:, :kk].long() - 5
+    assert (got_i >= 0).all() and (got_i < L).all()
+    assert torch.equal(torch.gather(z, 1, got_i), want_v)                     # every id points at a logit of that value
+    assert all(len(set(r.tolist())) == kk for r in got_i.cpu())               # no label twice
+    # ties are ordered by label id
+    same = vals[:, 1:kk] == vals[:, :kk - 1]
+    assert (got_i[:, 1:][same] > got_i[:, :-1][same]).all()
+    # where a value is unique in the row's top-k, the id is torch's id
+    uniq = torch.ones_like(want_v, dtype=torch.bool)
+    uniq[:, 1:] &= want_v[:, 1:] != want_v[:, :-1]
+    uniq[:, :-1] &= want_v[:, :-1] != want_v[:, 1:]
+    if kk == k:   # the last kept value may tie with one that was cut off
+        uniq[:, -1] &= (z == want_v[:, -1:]).sum(1) == 1
+    assert torch.equal(got_i[uniq], want_i[uniq])
