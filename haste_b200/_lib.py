@@ -5,7 +5,7 @@ CPU or PyTorch fallback.  Build it with ``python -m haste_b200.build``.
 """
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_uint64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_longlong, c_uint32, c_uint64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhaste_ffi.so")
@@ -43,6 +43,10 @@ SIGNATURES = {
     "haste_ffi_step": [P, P, I64, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64, U32, U32, P],
     "haste_topk_update": [P, I64, I64, I64, I64, I32, P, P, P],
     "haste_ffi_check_locations": [P, I64, I64, P],
+    "haste_ffi_set_max_ctas": [I32],
+    "haste_poll_status": [],
+    "haste_debug_set_wait_limit": [c_longlong],
+    "haste_debug_stall_next_step": [I32],
 }
 
 for _name, _args in SIGNATURES.items():

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libhaste_ffi.so")
-SOURCES = ["api.cu", "ffi_mma.cu", "ffi_step_sm100.cu", "ffi_forward_sm100.cu", "ffi_backward_sm100.cu", "elementwise.cu", "rewire.cu", "topk.cu"]
+SOURCES = ["api.cu", "runtime.cu", "ffi_mma.cu", "ffi_step_sm100_g128.cu", "ffi_step_sm100_g64.cu", "ffi_forward_sm100.cu", "ffi_backward_sm100.cu", "elementwise.cu", "rewire.cu", "topk.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
@@ -47,10 +47,6 @@ def _compile(src, force):
 
 
 def build(force=False, verbose=False):
-    extra = os.environ.get("HASTE_EXTRA_NVCC", "").split()      # development builds (e.g. -DHASTE_TRACE); forces a rebuild
-    if extra:
-        NVCC_FLAGS.extend(f for f in extra if f not in NVCC_FLAGS)
-        force = True
     os.makedirs(OBJ, exist_ok=True)
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         results = list(ex.map(lambda s: _compile(s, force), SOURCES))

@@ -32,16 +32,23 @@ int validate_shape(const char* who, int64_t B, int64_t D, int64_t F, int64_t L, 
   return HASTE_OK;
 }
 
-// Shape dispatch of the fused step: the tcgen05 kernel where its tile shapes apply (G=128, F=64, B%8==0,
-// no momentum), the warp-mma kernel for every other supported shape.  HASTE_STEP_IMPL=mma in the environment
-// forces the latter (used to compare the two kernels on the same inputs).
+// Shape dispatch of the fused step: the tcgen05 kernel where its tile shapes apply — (G=128, F=64) or (G=64, F=128),
+// B % 8 == 0 (16-byte rows of xt for the tensor map), D*B < 2^32 (32-bit dxt row offsets), L < 2^31 — the warp-mma
+// kernel for every other supported shape.
+static int g_max_ctas = 0;   // 0 = one CTA per SM
+
+static bool train_step_sm100_supported(int64_t B, int64_t D, int64_t F, int64_t L, int64_t G) {
+  return ((G == 128 && F == 64) || (G == 64 && F == 128)) && (B % 8) == 0 && D * B < (int64_t(1) << 32) && L < (int64_t(1) << 31);
+}
+
 int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
                       const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
                       cudaStream_t st, const StepDump* dump) {
-  static const bool force_mma = [] { const char* e = getenv("HASTE_STEP_IMPL"); return e != nullptr && strcmp(e, "mma") == 0; }();
-  if (!force_mma && train_step_sm100_supported(B, D, F, G, u))
-    return launch_train_step_sm100(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st, dump);
-  if (dump != nullptr) return fail(HASTE_ERR_UNSUPPORTED, "debug outputs exist only in the tcgen05 fused step (G=128, F=64, B%%8==0, no momentum)");
+  if (train_step_sm100_supported(B, D, F, L, G)) {
+    if (G == 128) return launch_train_step_sm100_g128f64(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, L, loss_kind, grad_scale, g_max_ctas, st, dump);
+    return launch_train_step_sm100_g64f128(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, L, loss_kind, grad_scale, g_max_ctas, st, dump);
+  }
+  if (dump != nullptr) return fail(HASTE_ERR_UNSUPPORTED, "debug outputs exist only in the tcgen05 fused step ((G,F) = (128,64) or (64,128), B%%8==0)");
   return launch_train_step_mma(loc, xt, tgt_ptr, tgt_ent, dxt, loss, u, B, D, F, L, G, loss_kind, grad_scale, st);
 }
 
@@ -57,7 +64,13 @@ using namespace haste;
 extern "C" {
 
 const char* haste_last_error_string(void) { return g_err; }
-int haste_version(void) { return 100; }
+int haste_version(void) { return 200; }
+
+int haste_ffi_set_max_ctas(int32_t n) {
+  if (n < 0) return fail(HASTE_ERR_BAD_ARG, "haste_ffi_set_max_ctas: n=%d < 0", n);
+  g_max_ctas = n;
+  return HASTE_OK;
+}
 
 int haste_ffi_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
                       int64_t L, int64_t G, int64_t ldz, haste_stream_t stream) {

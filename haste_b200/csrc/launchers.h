@@ -38,10 +38,14 @@ struct StepDump {
   void* dbias;   // bf16 [L]
 };
 
-bool train_step_sm100_supported(int64_t B, int64_t D, int64_t F, int64_t G, const UpdateArgs& u);
-int launch_train_step_sm100(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
-                            const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
-                            cudaStream_t st, const StepDump* dump = nullptr);
+// tcgen05 fused step: one translation unit per layer shape.  max_ctas > 0 caps the persistent grid (SMs left free for
+// kernels of other streams).
+int launch_train_step_sm100_g128f64(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt,
+                                    float* loss, const UpdateArgs& u, int64_t B, int64_t D, int64_t L, int loss_kind, float grad_scale,
+                                    int max_ctas, cudaStream_t st, const StepDump* dump);
+int launch_train_step_sm100_g64f128(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt,
+                                    float* loss, const UpdateArgs& u, int64_t B, int64_t D, int64_t L, int loss_kind, float grad_scale,
+                                    int max_ctas, cudaStream_t st, const StepDump* dump);
 int launch_train_step(const int32_t* loc, const void* xt, const int32_t* tgt_ptr, const uint32_t* tgt_ent, float* dxt, float* loss,
                       const UpdateArgs& u, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int loss_kind, float grad_scale,
                       cudaStream_t st, const StepDump* dump = nullptr);

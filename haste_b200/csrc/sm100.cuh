@@ -1,5 +1,6 @@
-// sm_100a primitives in inline PTX: mbarrier with bounded waits, tcgen05 (alloc / mma / commit / ld),
-// UMMA shared-memory and instruction descriptors, cp.async with zero fill, bulk reduce-add to global.
+// sm_100a primitives in inline PTX: mbarrier with bounded waits, TMA loads (tiled and tile::gather4, never
+// multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
+// zero fill, bulk reduce-add to global.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -16,6 +17,11 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// One arrival that also announces `bytes` of asynchronous (TMA) traffic: the phase completes when all arrivals
+// are in and that many bytes have landed.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -42,6 +48,7 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 // run to the end of their loops and the kernel exits normally.
 __device__ __noinline__ static bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
                                                   long long limit, unsigned sleep_ns) {
+  if (*abort_flag) return false;
   const long long t0 = clock64();
   for (;;) {
     // polling burst: the abort flag and the clock are looked at only between bursts
@@ -66,7 +73,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag, err, code, limit, sleep_ns);
 }
 
+// Bounded wait that ignores the abort flag: for work that has to finish before the CTA may exit (copies in flight
+// into its shared memory, tensor-core products writing its TMEM), also on the way out after an abort.
+__device__ __noinline__ static bool mbar_wait_final(uint32_t bar, uint32_t parity, long long limit) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait_hint(bar, parity, 4000u)) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---------------------------------------------------------------- TMA (this CTA's shared memory only, no multicast)
+// Tiled 2-D load of one box of the tensor map at element coordinates (x, y); x * element size must be a
+// multiple of 16 bytes.  Elements outside the tensor read as zero and still count towards the barrier's bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(tmap), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+// Four rows r0..r3 of a 2-D tensor (box = {columns, 1 row}) starting at column x, stacked as four consecutive rows
+// at dst; with a 128-byte box and the 128-byte swizzle each row lands exactly as the UMMA row-block layout wants it.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int x, int r0, int r1, int r2, int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+      : "memory");
+}
 
 // ---------------------------------------------------------------- cp.async (16 B, zero fill when !valid)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -200,6 +234,17 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_byte
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
   d |= 2ull << 61;
+  return d;
+}
+// Same, without swizzle (layout type 0), for a K-major operand: 8 rows x 16 bytes form one contiguous 128-byte core
+// matrix; the second 16-byte chunk along K (a K = 16 step of bf16 has two) lies lbo_bytes further, the next 8 rows
+// sbo_bytes further.
+__device__ __forceinline__ uint64_t make_sdesc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
   return d;
 }
 // Instruction descriptor for kind::f16: D fp32 (bit 4), A and B bf16 (bits 7, 10), A/B MN-major flags

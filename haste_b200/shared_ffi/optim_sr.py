@@ -14,6 +14,19 @@ class SRSgd(Optimizer):
                         stochastic_rounding=stochastic_rounding, seed=seed, rng=rng, contract=contract, step_count=0)
         super().__init__(params, defaults)
 
+    # keys this class adds to a parameter group; a state dict written by the reference's SRSgd has none of them
+    _EXTRA_GROUP_KEYS = dict(rng="reference", contract=True, step_count=0)
+
+    def __setstate__(self, state):
+        """``Optimizer.load_state_dict`` replaces the parameter groups with the saved ones.  Groups saved by the
+        reference's optimizer (keys lr, weight_decay, momentum, use_momentum, stochastic_rounding, seed:
+        shared_ffi/optim_sr.py:25-32) get the additive keys of this class back, at the values under which this class
+        behaves like the reference."""
+        super().__setstate__(state)
+        for group in self.param_groups:
+            for k, v in self._EXTRA_GROUP_KEYS.items():
+                group.setdefault(k, v)
+
     def _momentum_buf(self, p, needed):
         # The reference allocates an fp32 buffer for every parameter even with momentum off
         # (optim_sr.py:36-44); here it is created on first use only.

@@ -157,7 +157,7 @@ int haste_ffi_train_step(const int32_t* loc, const void* xt, void* w, void* bias
 
 /* Same step with debug outputs (tests): z_dump bf16 [B,ldz] receives the logits as the epilogue rounded them,
  * dw_dump bf16 [L,F] / dbias_dump bf16 [L] the gradients the update consumed; any of them may be NULL.
- * Only the tcgen05 kernel (G=128, F=64, B%8==0, no momentum) implements them; other shapes return
+ * Only the tcgen05 kernel ((G,F) = (128,64) or (64,128), B%8==0, no momentum) implements them; other shapes return
  * HASTE_ERR_UNSUPPORTED.  No counterpart in the reference (its logits and gradients are ordinary tensors). */
 int haste_ffi_train_step_dbg(const int32_t* loc, const void* xt, void* w, void* bias,
                              float* mom_w, float* mom_b,
@@ -167,6 +167,26 @@ int haste_ffi_train_step_dbg(const int32_t* loc, const void* xt, void* w, void* 
                              int32_t loss_kind, float grad_scale, float lr, float wd, float mu,
                              uint64_t seed, uint32_t step, uint32_t flags,
                              void* z_dump, int64_t ldz, void* dw_dump, void* dbias_dump, haste_stream_t stream);
+
+/* Cap the grid of the persistent fused-step kernel at n CTAs (0 = one per SM, the default).  A multi-GPU caller
+ * leaves a few SMs free this way, so that the collective of the previous step and the preparation of the next one,
+ * enqueued on other streams, run beside the kernel instead of after it.  Process-wide; no counterpart in the
+ * reference (it has neither a persistent kernel nor a collective on this path). */
+int haste_ffi_set_max_ctas(int32_t n);
+
+/* Status of the kernels with bounded device-side waits (the tcgen05 step, forward and backward).  A wait that runs
+ * out makes its kernel return by itself with its outputs invalid and records the fact; this call reports and clears
+ * it: HASTE_OK, or HASTE_ERR_TIMEOUT with the wait's id in the message.  Synchronise the stream first.  The next
+ * launch of one of those kernels reports a pending record too.  No counterpart in the reference (its kernels
+ * have no waits). */
+int haste_poll_status(void);
+
+/* Test hooks for the path above.  haste_debug_set_wait_limit: clock cycles a device-side wait may last (default
+ * 4e9, about two seconds).  haste_debug_stall_next_step: the next haste_ffi_train_step_dbg call withholds one
+ * barrier arrival at batch tile `tile` of every CTA, so that the waits behind it run out; nothing faults or
+ * traps, the kernel drains and returns. */
+int haste_debug_set_wait_limit(long long cycles);
+int haste_debug_stall_next_step(int32_t tile);
 
 /* Elementwise stochastic rounding fp32 -> bf16 with the reference stream over the flat index.
  * Replaces sr_triton.stochastic_rounding (shared_ffi/sr_triton.py:27-59). */

@@ -190,3 +190,25 @@ def test_two_rank_gloo_sharded_step(tmp_path, built_lib):
     for p in procs:
         out, _ = p.communicate(timeout=300)
         assert p.returncode == 0, out.decode()
+
+
+def test_srsgd_loads_reference_optimizer_state(built_lib):
+    """A state dict with the key set the reference's SRSgd writes (shared_ffi/optim_sr.py:25-44: six group keys and a
+    momentum_buf per parameter) loads, and the optimizer steps afterwards (the keys this class adds come back with
+    their reference-compatible defaults)."""
+    from haste_b200.shared_ffi.optim_sr import SRSgd
+    p = torch.nn.Parameter(torch.ones(4, 3))
+    opt = SRSgd([p], lr=0.1, weight_decay=0.0, momentum=0.9, seed=123)
+    ref_state = {
+        "state": {0: {"momentum_buf": torch.full((4, 3), 2.0)}},
+        "param_groups": [{"lr": 0.5, "weight_decay": 0.0, "momentum": 0.9, "use_momentum": True,
+                          "stochastic_rounding": True, "seed": 130, "params": [0]}],
+    }
+    opt.load_state_dict(ref_state)
+    g = opt.param_groups[0]
+    assert g["seed"] == 130 and g["rng"] == "reference" and g["contract"] is True and g["step_count"] == 0
+    p.grad = torch.ones(4, 3)
+    opt.step()                                    # fp32 parameter: the Python path, runs without a GPU
+    # momentum 0.9 * 2 + 1 = 2.8; p = 1 - 0.5 * 2.8
+    assert torch.allclose(p.data, torch.full((4, 3), 1.0 - 0.5 * 2.8))
+    assert opt.param_groups[0]["seed"] == 131 and opt.param_groups[0]["step_count"] == 1

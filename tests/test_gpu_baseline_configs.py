@@ -1,0 +1,71 @@
+"""GPU parity of the fused train step at the benchmark configurations themselves, through the public step call
+(``FusedFFIShard.step``: preparation launch + fused kernel) against the oracle's unfused restatement.
+
+Configuration 1 (the CPU-runnable one) runs at full size.  Configurations 2-5 keep their batch size, feature
+width, fan-in, group size, loss, feature distribution and target density (average positives, Zipf exponent) and cut
+only the label count, to about 20-30 thousand labels with a ragged last group (L % G != 0, L % 8 != 0), so that the
+oracle finishes in seconds.  Configuration 5's density (36 positives per row, Zipf 1.2, batch 1024) puts thousands of
+entries into the head group: the shared-memory target bitmap path.
+
+Tolerances: dX rel 1e-2 + abs 1e-3 of its magnitude (bf16 inputs, fp32 accumulation); loss rel 2e-3; updated weights
+and bias: at least 97 % bit-identical to the oracle's and none further than one bf16 step (the products differ from the
+oracle's in the last bits of the fp32 sum, which stochastic rounding turns into an occasional neighbouring bf16 value).
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import ffi_oracle as fo
+from oracle import philox as px
+
+CONFIGS = {
+    # name: B, D, L, F, G, avg positives, Zipf exponent, features, loss
+    "c1_full": (64, 768, 30938, 32, 32, 19.0, 1.1, "normal", "bce"),
+    "c2_cut": (512, 768, 64 * 312 + 33, 128, 64, 5.4, 1.1, "l2norm", "bce"),
+    "c3_cut": (512, 768, 128 * 200 + 11, 64, 128, 5.5, 1.0, "l2norm", "squared_hinge"),
+    "c4_cut": (256, 4096, 64 * 300 + 14, 128, 64, 4.8, 1.1, "relu", "bce"),
+    "c5_cut": (1024, 768, 128 * 250 + 1, 64, 128, 36.0, 1.2, "l2norm", "bce"),
+}
+
+
+def _step_vs_oracle(name, rng):
+    from haste_b200.fused import FusedFFIShard
+    B, D, L, F, G, avg, zipf, xk, loss = CONFIGS[name]
+    assert L % G != 0 and L % 8 != 0
+    inp = fo.make_inputs(B, D, L, F, G, avg, zipf, seed=42, x_kind=xk, bias_zero=True)
+    kind = fo.LOSS_SQHINGE if loss == "squared_hinge" else fo.LOSS_BCE
+    # the benchmark's scaling: squared hinge as a mean over [B,L] (src/runner.py:483), BCE as a sum (:469-478)
+    scale = 1.0 / (B * L) if loss == "squared_hinge" else 1.0
+    lr, wd, seed = 0.05, 1e-4, 123
+    shard = FusedFFIShard(inp["loc"].cuda(), inp["W"].clone().cuda(), inp["bias"].clone().cuda(), G, D, loss=loss, lr=lr,
+                          weight_decay=wd, seed=seed, rng=rng, grad_scale=scale)
+    dxt, loss_dev = shard.step(inp["X"].cuda(), inp["targets"].cuda())
+    torch.cuda.synchronize()
+    ref = fo.train_step(inp["loc"], inp["X"], inp["W"], inp["bias"], inp["targets"], G, kind, lr, wd, seed, step=0, grad_scale=scale,
+                        rng_mode=rng)
+    mag = float(ref["dXt"].abs().max())
+    err = (dxt.cpu() - ref["dXt"]).abs()
+    assert not (err > 1e-3 * mag + 1e-2 * ref["dXt"].abs()).any(), f"{name}: dX max err {float(err.max())} of {mag}"
+    assert abs(float(loss_dev) - ref["loss"]) <= 2e-3 * abs(ref["loss"]), (name, float(loss_dev), ref["loss"])
+    for got, want, what in ((shard.w, ref["W_new"], "weights"), (shard.bias, ref["bias_new"], "bias")):
+        gb, wb = fo._bf16_to_bits(got.cpu()), fo._bf16_to_bits(want)
+        same = gb == wb
+        assert same.mean() >= 0.97, f"{name}: only {same.mean():.4f} of the updated {what} match the oracle bit for bit"
+        g, w = px.bf16_bits_to_f32(gb).astype(np.float64), px.bf16_bits_to_f32(wb).astype(np.float64)
+        step = np.exp2(np.floor(np.log2(np.maximum(np.abs(w), 1e-30))) - 7)
+        assert (np.abs(g - w) <= step * 1.0001 + 1e-12)[~same].all(), f"{name}: an updated {what} value is more than one bf16 step off"
+    # a target-free label far from the head keeps "weight decay only" semantics: its gradient is the loss gradient of
+    # negatives, which is what the bulk of the layer sees — covered by the comparison above.  The ragged tail:
+    assert shard.w.shape[0] == L
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_fused_step_at_benchmark_configuration(name):
+    _step_vs_oracle(name, "packed")
+
+
+def test_fused_step_config1_reference_stream():
+    """Configuration 1 with the reference's own random stream (tl.randint keyed by the optimizer's seed)."""
+    _step_vs_oracle("c1_full", "reference")

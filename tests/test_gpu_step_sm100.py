@@ -1,4 +1,5 @@
-"""GPU parity tests of the tcgen05 fused train step (group size 128, fan-in 64) through the C ABI.
+"""GPU parity tests of the tcgen05 fused train step (group size 128 / fan-in 64, and group size 64 / fan-in 128)
+through the C ABI.
 
 The kernel's debug outputs expose the bf16 logits and the bf16 gradients it consumed, which splits the check
 into (a) tensor-core products against the oracle within the floating-point tolerance (rel 1e-2 / abs 1e-3 of
@@ -14,6 +15,8 @@ from oracle import ffi_oracle as fo
 
 F, G = 64, 128
 SHAPES = [(200, 256, 1111), (512, 768, 5000), (128, 128, 384), (1024, 300, 2000), (8, 96, 100), (392, 768, 20000)]  # B, D, L
+KINDS = [(128, 64), (64, 128)]          # (G, F) with a tcgen05 fused step
+SHAPES_G64 = [(200, 256, 1111), (512, 768, 5000), (64, 128, 192), (1024, 300, 2000), (8, 160, 100), (256, 4096, 3018)]  # B, D, L
 
 
 @pytest.fixture(scope="module")
@@ -33,7 +36,7 @@ def _close(got, want, rel, abs_, what):
     assert not bad.any(), f"{what}: {int(bad.sum())}/{bad.numel()} outside tolerance, max err {float((got - want).abs().max())}"
 
 
-def _run(ffi, lib, inp, B, D, L, kind, scale, rng, label0=0, bias=True, step=3, seed=123, lr=0.05, wd=1e-4):
+def _run(ffi, lib, inp, B, D, L, kind, scale, rng, label0=0, bias=True, step=3, seed=123, lr=0.05, wd=1e-4, G=G):
     dev = {k: v.cuda() for k, v in inp.items()}
     xt = dev["X"].t().contiguous()
     NG = (L + G - 1) // G
@@ -53,14 +56,17 @@ def _run(ffi, lib, inp, B, D, L, kind, scale, rng, label0=0, bias=True, step=3, 
     return w, b, dxt, float(loss), z, dw, db
 
 
-@pytest.mark.parametrize("shape", SHAPES)
+_CHAIN = [(128, 64, s) for s in SHAPES] + [(64, 128, s) for s in SHAPES_G64]
+
+
+@pytest.mark.parametrize("case", _CHAIN, ids=[f"G{c[0]}F{c[1]}-B{c[2][0]}D{c[2][1]}L{c[2][2]}" for c in _CHAIN])
 @pytest.mark.parametrize("rng", ["packed", "reference"])
-def test_sm100_step_hinge_chain(hb, shape, rng):
+def test_sm100_step_hinge_chain(hb, case, rng):
     ffi, lib = hb
-    B, D, L = shape
+    G, F, (B, D, L) = case
     inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=B + L, x_kind="normal", bias_zero=False)
     scale, label0 = 0.5, 384
-    w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, scale, rng, label0=label0)
+    w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, scale, rng, label0=label0, G=G)
     # (a) tensor-core products within tolerance
     z_ref = fo.forward(inp["loc"], inp["X"], inp["W"], inp["bias"], G, round_bf16=False)
     _close(z, z_ref, 1e-2, 1e-3 * max(1.0, float(z_ref.abs().max())), "logits")
@@ -79,20 +85,22 @@ def test_sm100_step_hinge_chain(hb, shape, rng):
     assert np.array_equal(_bits(b), fo._bf16_to_bits(want_b)), "bias"
 
 
-@pytest.mark.parametrize("shape", [(200, 256, 1111), (512, 768, 5000), (8, 96, 100)])
-def test_sm100_step_bce_and_nobias(hb, shape):
+@pytest.mark.parametrize("kind", KINDS, ids=["G128F64", "G64F128"])
+@pytest.mark.parametrize("shape", [(200, 256, 1111), (512, 768, 5000), (8, 160, 100)])
+def test_sm100_step_bce_and_nobias(hb, shape, kind):
     ffi, lib = hb
     B, D, L = shape
+    G, F = kind
     inp = fo.make_inputs(B, D, L, F, G, 12, 1.1, seed=7, x_kind="normal", bias_zero=False)
     for bias in (True, False):
-        w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_BCE, 1.0, "packed", bias=bias)
+        w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_BCE, 1.0, "packed", bias=bias, G=G)
         bias_t = inp["bias"] if bias else None
         z_ref = fo.forward(inp["loc"], inp["X"], inp["W"], bias_t, G, round_bf16=False)
         _close(z, z_ref, 1e-2, 1e-3 * max(1.0, float(z_ref.abs().max())), "logits")
         loss_ref, dY = fo.loss_and_grad(z.cpu(), inp["targets"], fo.LOSS_BCE, 1.0)
         assert abs(loss - loss_ref) <= 2e-3 * abs(loss_ref)
         dw_ref = fo.backward_weights(inp["loc"], inp["X"], dY, G, L, round_bf16=False)
-        _close(dw, dw_ref, 2e-2, 2e-3 * max(1.0, float(dw_ref.abs().max())), "dW")      # sigmoid via fast exp: dY may differ by a bf16 step
+        _close(dw, dw_ref, 2e-2, 2e-3 * max(1.0, float(dw_ref.abs().max())), "dW")      # sigmoid via tanh.approx: dY may differ by a bf16 step
         dxt_ref = fo.backward_features(inp["loc"], inp["W"], dY, G, D)
         _close(dxt, dxt_ref, 2e-2, 2e-3 * max(1.0, float(dxt_ref.abs().max())), "dXt")
         want_w, _ = fo.sgd_update(inp["W"], dw.cpu(), None, 0.05, 1e-4, 0.0, False, True, fo.rand16_for((L, F), 123, 3, "packed", 0))
@@ -182,3 +190,62 @@ def test_sm100_step_rank_count_independent(hb, loss):
     dxt_sum = sum(p[2] for p in parts)
     _close(dxt_sum, dxt_all, 1e-4, 1e-5 * float(dxt_all.abs().max()), "dX summed over ranks")
     assert abs(sum(p[3] for p in parts) - loss_all) <= 1e-4 * abs(loss_all) + 1e-6
+
+
+@pytest.mark.parametrize("kind", KINDS, ids=["G128F64", "G64F128"])
+def test_sm100_step_momentum(hb, kind):
+    """Momentum (the reference's Amazon-3M run uses 0.9) inside the fused step: the debug step yields the gradients
+    the update consumes (they do not depend on the optimizer), the production step then runs with preset momentum
+    buffers; weights, bias and both buffers must equal the oracle's update of those gradients bit for bit."""
+    ffi, lib = hb
+    G, F = kind
+    B, D, L = 256, 384, 1000
+    lr, wd, mu, seed, step = 0.05, 1e-4, 0.9, 123, 5
+    inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=21, x_kind="normal", bias_zero=False)
+    _, _, _, _, _, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_BCE, 1.0, "packed", step=step, G=G)
+    dev = {k: v.cuda() for k, v in inp.items()}
+    xt = dev["X"].t().contiguous()
+    NG = (L + G - 1) // G
+    ptr = torch.zeros(NG + 1, dtype=torch.int32, device="cuda")
+    ent = torch.zeros(max(1, dev["targets"].shape[0]), dtype=torch.int32, device="cuda")
+    ffi.targets_bucket(dev["targets"], 0, L, G, ptr, ent, torch.zeros(NG, dtype=torch.int32, device="cuda"))
+    gen = torch.Generator().manual_seed(3)
+    mom_w0 = torch.randn(L, F, generator=gen) * 0.01
+    mom_b0 = torch.randn(L, generator=gen) * 0.01
+    w, b, mom_w, mom_b = dev["W"].clone(), dev["bias"].clone(), mom_w0.cuda(), mom_b0.cuda()
+    dxt = torch.empty(D, B, dtype=torch.float32, device="cuda")
+    flags = ffi.make_flags(sr=True, contract=True, rng="packed", zero_dxt=True, loss=False)
+    ffi.train_step(dev["loc"], xt, w, b, mom_w, mom_b, ptr, ent, dxt, None, G, 0, lib.LOSS_BCE, 1.0, lr, wd, mu, seed, step, flags)
+    torch.cuda.synchronize()
+    want_w, want_mw = fo.sgd_update(inp["W"], dw.cpu(), mom_w0, lr, wd, mu, True, True, fo.rand16_for((L, F), seed, step, "packed", 0))
+    want_b, want_mb = fo.sgd_update(inp["bias"], db.cpu(), mom_b0, lr, wd, mu, True, True,
+                                    fo.rand16_for((L, 1), seed, step, "packed", 0, is_bias=True).reshape(L))
+    assert np.array_equal(_bits(w), fo._bf16_to_bits(want_w)), "weights"
+    assert np.array_equal(_bits(b), fo._bf16_to_bits(want_b)), "bias"
+    assert torch.equal(mom_w.cpu(), want_mw), "weight momentum"
+    assert torch.equal(mom_b.cpu(), want_mb), "bias momentum"
+
+
+def test_sm100_step_wait_runs_out_and_recovers(hb):
+    """The bounded-wait path: with a 1 ms wait limit and one barrier arrival withheld, the kernel returns by itself
+    (no trap, no fault), the status poll reports HASTE_ERR_TIMEOUT exactly once, and the next step — TMEM was freed,
+    the context is intact — runs normally and matches the oracle."""
+    ffi, lib = hb
+    B, D, L = 512, 256, 128 * 300
+    inp = fo.make_inputs(B, D, L, F, G, 4, 1.1, seed=9, bias_zero=False)
+    assert lib.lib.haste_poll_status() == lib.OK
+    try:
+        assert lib.lib.haste_debug_set_wait_limit(2_000_000) == lib.OK       # about 1 ms
+        assert lib.lib.haste_debug_stall_next_step(1) == lib.OK
+        _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, 1.0, "packed")          # returns by itself; outputs invalid
+    finally:
+        lib.lib.haste_debug_set_wait_limit(4_000_000_000)
+    assert lib.lib.haste_poll_status() == lib.ERR_TIMEOUT
+    assert "wait id" in lib.last_error()
+    assert lib.lib.haste_poll_status() == lib.OK                               # reported once
+    w, b, dxt, loss, z, dw, db = _run(ffi, lib, inp, B, D, L, lib.LOSS_SQHINGE, 1.0, "packed")
+    assert lib.lib.haste_poll_status() == lib.OK
+    z_ref = fo.forward(inp["loc"], inp["X"], inp["W"], inp["bias"], G, round_bf16=False)
+    _close(z, z_ref, 1e-2, 1e-3 * max(1.0, float(z_ref.abs().max())), "logits after recovery")
+    want_w, _ = fo.sgd_update(inp["W"], dw.cpu(), None, 0.05, 1e-4, 0.0, False, True, fo.rand16_for((L, F), 123, 3, "packed", 0))
+    assert np.array_equal(_bits(w), fo._bf16_to_bits(want_w))
