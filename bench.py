@@ -8,15 +8,23 @@ For N > 1 launch one rank per GPU:
         bench.py --gpus N --steps K --warmup W
 
 A "step" is one pass of the fused train step over one synthetic batch.  Rank 0 prints ONE JSON line.
-  value     whole-job samples/s with the batch already resident in HBM, device-timed (CUDA events per step,
-            L2 flushed between steps, max over ranks)
+  value     whole-job samples/s with the batch already resident in HBM, device-timed: one CUDA-event pair per step on
+            the launching stream, L2 flushed between steps outside the pairs; the per-step times are reduced with
+            MAX over the ranks, ms_per_step is their median (the mean is reported beside it)
   e2e       same metric through the public API from pinned HOST buffers: host->device copy of the batch and
             device->host read of the loss inside the timed region
   roofline  the fused train-step kernel alone: 6*B*L*F flops / its CUDA-event duration, against the measured
             dense bf16 peak
   cpu_baseline  the CPU restatement (oracle/cpu_step.py) timed on this box's host cores on a bounded sample
 Labels are sharded contiguously by group over the ranks (strong scaling: the layer is fixed, each rank owns
-1/N of it), features are replicated, and the per-rank feature gradients are summed by one NCCL all-reduce.
+1/N of it), features are replicated, and the per-rank feature gradients are summed by one NCCL all-reduce.  At N > 1
+the step is pipelined over three streams (ShardedFFILayer.step_pipelined): the all-reduce of step i-1 and the
+preparation of batch i+1 run beside the fused kernel of step i, which leaves a few SMs free for them; everything a
+step enqueues finishes inside that step's event pair, and the last all-reduce inside the last one.
+
+--impl reference: the reference's own CUDA kernels (compiled from its sources into oracle/_ref, legacy wmma code on
+this GPU) driven as its autograd function and training loop drive them, PyTorch ops for what the reference does in
+PyTorch; falls back to the CPU restatement when that build or a GPU is absent.
 """
 import argparse
 import json
@@ -35,9 +43,17 @@ import torch
 METRIC = "FFI train-step samples/s @670K labels fan_in=64 B=512; % tensor/HBM roofline"
 LR, WD, SEED = 0.05, 1e-4, 123
 N_BATCHES = 4
-# dram bytes (read+write) of one fused-step launch from an ncu capture; filled per workload when a capture exists
-# (see profiles/); None = not captured yet.
-NCU_TRAFFIC_BYTES = {"c3": 126.7e6}   # ncu capture of one launch at C3: dram read 90.9 MB + write 35.8 MB
+
+
+def ncu_traffic_bytes(workload):
+    """dram read+write bytes of one fused-step launch, from the ncu capture recorded in profiles/ncu_traffic.json
+    (None when no capture of this workload is on record)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        rec = json.load(open(path)).get(workload)
+        return None if rec is None else float(rec["dram_bytes_read"]) + float(rec["dram_bytes_write"])
+    except Exception:
+        return None
 
 
 def measured_peaks():
@@ -105,6 +121,109 @@ def build_problem(wl, rank, world, device):
     return c, layer, batches, (loc, W, bias, grad_scale)
 
 
+def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, clocks_index=None):
+    """Device-timed steps of the given layer: returns (per-step ms as MAX over ranks, wall seconds, clock summary)."""
+    stream = torch.cuda.current_stream(device)
+    pipelined = world > 1
+
+    def one(i, last=False):
+        x, t = dev_batches[i % N_BATCHES]
+        if pipelined:
+            layer.step_pipelined(x, t, next_batch=None if last else dev_batches[(i + 1) % N_BATCHES], want_loss=True)
+            if last:
+                layer.flush()            # the last all-reduce belongs to the last timed step
+        else:
+            layer.step(x, t, want_loss=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for i in range(warmup):
+        flush.zero_()
+        one(i)
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    sampler = ClockSampler(clocks_index) if clocks_index is not None else None
+    if sampler:
+        sampler.__enter__()
+    t_wall0 = time.perf_counter()
+    for i in range(steps):
+        flush.zero_()
+        ev[i][0].record(stream)
+        one(warmup + i, last=(i == steps - 1))
+        ev[i][1].record(stream)
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    if sampler:
+        sampler.__exit__()
+    ms = torch.tensor([a.elapsed_time(b) for a, b in ev], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.tolist(), t_wall, (sampler.summary() if sampler else None)
+
+
+def _time_kernel(shard, x, t, device, flush, n, dist, world):
+    """The fused kernel alone: events around the single launch, inputs prepared through the unfused entry points, L2
+    flushed.  Returns (MAX over ranks of the mean ms, per-rank means)."""
+    from haste_b200 import ffi as hffi
+    stream = torch.cuda.current_stream(device)
+    xt = hffi.transpose_bf16(x)
+    shard.bucket_targets(t)
+    dxt = torch.zeros(xt.shape, dtype=torch.float32, device=device)
+    kern_ms = []
+    for i in range(3 + n):
+        flush.zero_()
+        seed, stp = shard._keys()
+        flags = hffi.make_flags(sr=True, contract=True, rng=shard.rng, zero_dxt=False, loss=True)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dxt.zero_()
+        a.record(stream)
+        hffi.train_step(shard.loc, xt, shard.w, shard.bias, None, None, shard.tgt_ptr, shard.tgt_ent, dxt, shard.loss_buf,
+                        shard.G, shard.label0, shard.loss_kind, shard.grad_scale, LR, WD, 0.0, seed, stp, flags)
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        if i >= 3:
+            kern_ms.append(a.elapsed_time(b))
+    kern = torch.tensor([statistics.mean(kern_ms)], dtype=torch.float64, device=device)
+    ranks = [float(kern)]
+    if world > 1:
+        gathered = [torch.zeros_like(kern) for _ in range(world)]
+        dist.all_gather(gathered, kern)
+        ranks = [float(g) for g in gathered]
+        dist.all_reduce(kern, op=dist.ReduceOp.MAX)
+    return float(kern), ranks
+
+
+def _check_ranks_agree(layer, x, t, device, dist, world):
+    """What the N ranks computed, checked outside every timed region: each rank's partial dX (its label shard) is
+    summarised by two checksums (plain sum, and sum weighted by a fixed pattern), the checksums are all-gathered,
+    and their sum must equal the checksums of the all-reduced dX on every rank.  Returns "ok" or raises."""
+    dxt, _ = layer.shard.step(x, t, want_loss=False)
+    torch.cuda.synchronize(device)
+    pat = torch.linspace(0.5, 1.5, dxt.numel(), dtype=torch.float64, device=device).view_as(dxt)
+    part = torch.stack([dxt.double().sum(), (dxt.double() * pat).sum(), dxt.double().abs().sum()])
+    red = dxt.clone()
+    dist.all_reduce(red, op=dist.ReduceOp.SUM)
+    full = torch.stack([red.double().sum(), (red.double() * pat).sum()])
+    parts = [torch.zeros_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    want = sum(p[:2] for p in parts)
+    scale = sum(float(p[2]) for p in parts) + 1e-30
+    err = float((full - want).abs().max()) / scale
+    if not err <= 1e-5:
+        raise RuntimeError(f"rank results disagree: reduced dX checksum differs from the sum of the partial checksums by {err:.3e} (relative)")
+    # every rank holds the same reduced tensor
+    same = torch.stack([red.double().sum(), (red.double() * pat).sum()])
+    lo, hi = same.clone(), same.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    if not torch.equal(lo, hi):
+        raise RuntimeError("the all-reduced dX differs between ranks")
+    return "ok"
+
+
 def run_ours(args):
     import torch.distributed as dist
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -115,7 +234,6 @@ def run_ours(args):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    from haste_b200 import ffi as hffi
     c, layer, batches, full = build_problem(args.workload, rank, world, device)
     shard = layer.shard
     B, D = c["B"], c["D"]
@@ -129,56 +247,20 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    # ---------------- device-resident steps: per-step CUDA events, L2 flushed in between
-    def device_step(i):
-        x, t = dev_batches[i % N_BATCHES]
-        return layer.step(x, t, want_loss=True)
-
-    for i in range(args.warmup):
-        flush.zero_()
-        device_step(i)
-    barrier()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    with ClockSampler(local) as clocks:
-        t_wall0 = time.perf_counter()
-        for i in range(args.steps):
-            flush.zero_()
-            ev[i][0].record(stream)
-            device_step(i)
-            ev[i][1].record(stream)
+    if world > 1:
+        # the first collectives of a communicator set up channels and buffers: keep that out of every timed step
+        warm = torch.zeros(D, B, dtype=torch.float32, device=device)
+        for _ in range(25):
+            dist.all_reduce(warm)
         barrier()
-        t_wall = time.perf_counter() - t_wall0
-    step_ms = [a.elapsed_time(b) for a, b in ev]
-    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(total_ms) / args.steps
 
-    # ---------------- the fused kernel alone (roofline): events around the single launch, L2 flushed
-    xt = hffi.transpose_bf16(dev_batches[0][0])
-    shard.bucket_targets(dev_batches[0][1])
-    kern_ms = []
-    for i in range(3 + min(args.steps, 20)):
-        flush.zero_()
-        seed, stp = shard._keys()
-        flags = hffi.make_flags(sr=True, contract=True, rng=shard.rng, zero_dxt=False, loss=True)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        shard._dxt.zero_()
-        a.record(stream)
-        hffi.train_step(shard.loc, xt, shard.w, shard.bias, None, None, shard.tgt_ptr, shard.tgt_ent, shard._dxt, shard.loss_buf,
-                        shard.G, shard.label0, shard.loss_kind, shard.grad_scale, LR, WD, 0.0, seed, stp, flags)
-        b.record(stream)
-        torch.cuda.synchronize(device)
-        if i >= 3:
-            kern_ms.append(a.elapsed_time(b))
-    kern = torch.tensor([statistics.mean(kern_ms)], dtype=torch.float64, device=device)
-    kern_ranks = [float(kern)]
-    if world > 1:
-        gathered = [torch.zeros_like(kern) for _ in range(world)]
-        dist.all_gather(gathered, kern)
-        kern_ranks = [float(g) for g in gathered]
-        dist.all_reduce(kern, op=dist.ReduceOp.MAX)
-    kern_ms_avg = float(kern)
+    # ---------------- device-resident steps: per-step CUDA events, L2 flushed in between
+    step_ms, t_wall, clocks = _time_steps(layer, dev_batches, args.steps, args.warmup, world, device, flush, dist, clocks_index=local)
+    ms_per_step = statistics.median(step_ms)
+    ms_mean = statistics.mean(step_ms)
+
+    # ---------------- the fused kernel alone (roofline)
+    kern_ms_avg, kern_ranks = _time_kernel(shard, dev_batches[0][0], dev_batches[0][1], device, flush, min(args.steps, 20), dist, world)
 
     # ---------------- end to end from pinned host buffers (H2D of the batch, D2H of the loss, every step)
     # Two device-side input slots: the copy of batch i+1 is enqueued on a copy stream while step i runs, as a
@@ -204,7 +286,11 @@ def run_ours(args):
         s_ = i & 1
         nnz = host_batches[i % N_BATCHES][1].shape[0]
         stream.wait_event(copied[s_])
-        _, loss = layer.step(xbuf[s_], tbuf[s_][:nnz], want_loss=True)
+        if world > 1:
+            # the previous step's all-reduce runs beside this step's kernel; this batch is prepared on this stream
+            _, loss = layer.step_pipelined(xbuf[s_], tbuf[s_][:nnz], next_batch=None, want_loss=True)
+        else:
+            _, loss = layer.step(xbuf[s_], tbuf[s_][:nnz], want_loss=True)
         consumed[s_].record(stream)
         loss_host.copy_(loss, non_blocking=True)
         enqueue_copy(i + 1)                               # overlaps this step's kernels
@@ -218,48 +304,93 @@ def run_ours(args):
     for i in range(args.warmup):
         e2e_step(i)
     barrier()
-    e2e_s = 0.0
+    e2e_times = []
     for i in range(args.warmup, args.warmup + args.steps):
         flush.zero_()
-        barrier()
+        barrier()                                         # ranks start each step together; outside the timed region
         t0 = time.perf_counter()
         e2e_step(i)
-        e2e_s += time.perf_counter() - t0
-    e2e_t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+        e2e_times.append(time.perf_counter() - t0)
+    if world > 1:
+        layer.flush()
+    e2e_t = torch.tensor(e2e_times, dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(e2e_t) * 1e3 / args.steps
+    e2e_ms = statistics.median(e2e_t.tolist()) * 1e3
     h2d = B * D * 2 + int(statistics.mean(t.shape[0] for _, t in batches)) * 8
+
+    # ---------------- N > 1: what the ranks computed, and the 2.8M-label workload in the same process
+    parity_n, c5 = None, None
+    if world > 1:
+        parity_n = _check_ranks_agree(layer, dev_batches[0][0], dev_batches[0][1], device, dist, world)
+        if args.workload == "c3" and not args.no_c5:
+            c5 = _c5_lines(args, rank, world, device, flush, dist)
 
     if rank == 0:
         peaks = measured_peaks()
         flops = 6.0 * B * c["L"] * c["F"]                       # whole layer, all ranks
         flops_rank = flops * (shard.L / c["L"])
         achieved = flops_rank / (kern_ms_avg * 1e-3) / 1e12
+        launches_per_step = 2 if world == 1 else 2            # preparation launch + fused kernel (the collective is NCCL's)
         line = {
             "metric": METRIC, "value": B / (ms_per_step * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "ms_per_step_mean": ms_mean, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={B} D={D} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']} "
-                                   f"SR-SGD lr={LR} wd={WD} momentum=0 rng=packed",
-                       "parallelism": f"labels sharded over {world} rank(s), features replicated, dX all-reduce",
-                       "l2": "flushed between steps (256 MiB write) outside the timed regions; value: per-step CUDA events, e2e: per-step wall clock",
+            "config": {"workload": _workload_string(args.workload, c) + " rng=packed",
+                       "parallelism": (f"labels sharded over {world} rank(s), features replicated, dX all-reduce"
+                                       + ("" if world == 1 else f"; pipelined: all-reduce of step i-1 and preparation of batch i+1 run beside the kernel of "
+                                          f"step i ({layer.reserve_sms} SMs left free), all of it inside step i's timed region, the last all-reduce inside the last step")),
+                       "l2": "flushed between steps (256 MiB write) outside the timed regions; value: median of per-step CUDA-event times (MAX over ranks), e2e: median per-step wall clock",
                        "layer_tflops": flops / (ms_per_step * 1e-3) / 1e12},
             "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms},
-            "gpu_launches": 2 * args.steps,
-            "clocks": clocks.summary(),
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": ncu_traffic_bytes(args.workload) if world == 1 else None,
                          "kernel": "fused train step", "kernel_ms": kern_ms_avg, "kernel_ms_ranks": [round(k, 4) for k in kern_ranks], "peak_source": peaks["source"] + " burst bf16"},
             "wall_s_timed_region": t_wall,
         }
+        if parity_n is not None:
+            line["parity_n"] = parity_n
+        if c5 is not None:
+            line["c5"] = c5
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, full, batches, budget_s=20.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _c5_lines(args, rank, world, device, flush, dist):
+    """The 2.8M-label workload (B=1024, BCE) on the same ranks, and on rank 0 alone for the ratio: the scale-out
+    target is stated on this workload.  Fewer steps than the main line (a step is ten times longer)."""
+    steps, warmup = max(5, min(args.steps, 30)), 3
+    c, layer, batches, _ = build_problem("c5", rank, world, device)
+    dev_batches = [(x.to(device), t.to(device)) for x, t in batches]
+    ms, _, _ = _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist)
+    kern, kern_ranks = _time_kernel(layer.shard, dev_batches[0][0], dev_batches[0][1], device, flush, 5, dist, world)
+    parity = _check_ranks_agree(layer, dev_batches[0][0], dev_batches[0][1], device, dist, world)
+    del layer
+    torch.cuda.empty_cache()
+    out = {"value": c["B"] / (statistics.median(ms) * 1e-3), "unit": "samples/s", "ms_per_step": statistics.median(ms), "steps": steps,
+           "kernel_ms_ranks": [round(k, 4) for k in kern_ranks], "parity_n": parity,
+           "workload": f"c5: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']}"}
+    # one GPU, same process: rank 0 holds the whole layer and uses every SM, the other ranks wait
+    n1 = torch.zeros(1, dtype=torch.float64, device=device)
+    if rank == 0:
+        from haste_b200 import _lib
+        _lib.check(_lib.lib.haste_ffi_set_max_ctas(0), "set_max_ctas")
+        _, layer1, _, _ = build_problem("c5", 0, 1, device)
+        ms1, _, _ = _time_steps(layer1, dev_batches, max(5, steps // 3), 3, 1, device, flush, dist)
+        n1[0] = statistics.median(ms1)
+        del layer1
+        torch.cuda.empty_cache()
+    dist.all_reduce(n1, op=dist.ReduceOp.MAX)
+    out["n1_ms_per_step"] = float(n1)
+    out["vs_n1"] = float(n1) / out["ms_per_step"]
+    return out
 
 
 def cpu_baseline(wl, full, batches, budget_s=20.0, steps=3):
@@ -293,29 +424,136 @@ def cpu_baseline(wl, full, batches, budget_s=20.0, steps=3):
     t_step = statistics.median(times) * (NG / ng)
     return {"value": c["B"] / t_step, "unit": "samples/s", "cores": cores, "kind": "port",
             "sample": f"first {ng} of {NG} label groups ({Ls} labels), full batch, {len(times)} timed steps, scaled x{NG / ng:.2f}",
-            "ms_per_step_scaled": t_step * 1e3}
+            "ms_per_step_scaled": t_step * 1e3, "timed_steps": len(times)}
+
+
+def _workload_string(wl, c):
+    return (f"{wl}: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']} "
+            f"SR-SGD lr={LR} wd={WD} momentum=0")
+
+
+def reference_gpu_step_fn(ref, c, loc, W, bias, device):
+    """The reference's training step for this layer, driven the way its own code drives it: its CUDA kernels through
+    an autograd function that restates shared_ffi/bindings.py:12-54 (transpose, forward kernel; backward: bias
+    gradient by a column sum, backward-features kernel + transpose, backward-weights kernel), the loss written with
+    PyTorch ops as src/runner.py:469-483 does, and PyTorch ops where the reference calls its Triton kernels, which
+    cannot run unmodified on this Triton version (shared_ffi/sr_triton.py:13): the stochastic rounding of dX becomes
+    a cast, the fused SGD + stochastic-rounding update one in-place elementwise pass with the same memory traffic
+    (weights read and written, gradient read).  Shapes outside the reference's launch limits (group size 128, and
+    (64,128) whose launch exceeds 48 KB of shared memory) run at group size 32 on an index table with repeated rows."""
+    G, F, L, B, D = c["G"], c["F"], c["L"], c["B"], c["D"]
+    gs = G if (G in (16, 32, 64) and not (G == 64 and F == 128)) else 32
+    loc_r = (loc if gs == G else loc.repeat_interleave(G // gs, 0)).contiguous().to(device)
+    Wp = torch.nn.Parameter(W.to(device))
+    bp = torch.nn.Parameter(bias.to(device))
+
+    class RefFFI(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, w, b):
+            xt = x.t().contiguous()
+            ctx.save_for_backward(xt, w)
+            return ref.ffi_forward_cuda(loc_r, xt, w, b, B, D, F, L, gs)
+
+        @staticmethod
+        def backward(ctx, gz):
+            xt, w = ctx.saved_tensors
+            gz = gz.contiguous()
+            gb = gz.sum(0)
+            gx = ref.ffi_backward_features_cuda(xt, w, loc_r, gz, B, D, F, L, gs).t().contiguous().to(torch.bfloat16)
+            gw = ref.ffi_backward_weights_cuda(xt, w, loc_r, gz, B, D, F, L, gs)
+            return gx, gw, gb
+
+    def loss_fn(z, tg):
+        rows, cols = tg[:, 0].long(), tg[:, 1].long()
+        if c["loss"] == "bce":
+            loss = z.clamp(min=0.0).sum(dtype=torch.float32)
+            loss = loss - z[rows, cols].sum(dtype=torch.float32)
+            return loss + (1 + (-torch.abs(z)).exp()).log().sum(dtype=torch.float32)
+        zf = z.float()                      # squared hinge, mean over [B,L]: negatives everywhere, positives corrected
+        t = (1.0 + zf).clamp(min=0.0)
+        zp = zf[rows, cols]
+        tot = (t * t).sum() + ((1.0 - zp).clamp(min=0.0) ** 2 - (1.0 + zp).clamp(min=0.0) ** 2).sum()
+        return tot / (B * L)
+
+    def step(x, tg):
+        x = x.detach().requires_grad_(True)
+        z = RefFFI.apply(x, Wp, bp)
+        loss = loss_fn(z, tg)
+        loss.backward()
+        with torch.no_grad():
+            Wp.add_(Wp.grad, alpha=-LR)
+            bp.add_(bp.grad, alpha=-LR)
+        Wp.grad = None
+        bp.grad = None
+        return x.grad, loss
+
+    return step
 
 
 def run_reference(args):
-    """Reference arm.  The reference ships no CPU implementation of this path and its CUDA extension is not part
-    of this repository, so this arm times the CPU restatement (oracle/cpu_step.py) with every host thread on a
-    bounded sample of the same workload."""
+    """Reference arm (rank 0 only): the reference's CUDA kernels from oracle/_ref on this GPU when that build and a GPU
+    are present, else the CPU restatement (oracle/cpu_step.py) with every host thread on a bounded sample."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
     from haste_b200 import synth
+    from oracle import build_ref
     c = synth.WORKLOADS[args.workload]
     loc, W, bias = synth.make_layer(c["D"], c["L"], c["F"], c["G"], seed=42)
     grad_scale = 1.0 / (c["B"] * c["L"]) if c["loss"] == "squared_hinge" else 1.0
-    batches = [synth.make_batch(c["B"], c["D"], c["L"], c["avg_pos"], c["zipf"], c["x"], seed=1000 + i) for i in range(2)]
-    cb = cpu_baseline(args.workload, (loc, W, bias, grad_scale), batches, budget_s=60.0, steps=max(1, min(args.steps, 5)))
-    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "samples/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step_scaled"], "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']} "
-                                   f"SR-SGD lr={LR} wd={WD} momentum=0 rng=packed"},
-            "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    batches = [synth.make_batch(c["B"], c["D"], c["L"], c["avg_pos"], c["zipf"], c["x"], seed=1000 + i) for i in range(N_BATCHES)]
+    config = {"workload": _workload_string(args.workload, c) + " rng=packed",
+              "parallelism": "one GPU (rank 0 alone runs the reference arm)",
+              "l2": "flushed between steps (256 MiB write) outside the timed regions"}
+    ref = build_ref.load() if torch.cuda.is_available() else None
+    if ref is not None and c["B"] * c["L"] >= 2 ** 31:
+        ref = None                                   # the reference indexes [B,L] with 32-bit ints
+    if ref is None:
+        steps = max(1, min(args.steps, 5))
+        cb = cpu_baseline(args.workload, (loc, W, bias, grad_scale), batches, budget_s=60.0, steps=steps)
+        config["note"] = "CPU restatement on a bounded sample; ms_per_step is extrapolated to the whole layer (see cpu_baseline.sample)"
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "samples/s", "n_gpus": args.gpus,
+                "steps": cb["timed_steps"], "warmup": 1, "ms_per_step": cb["ms_per_step_scaled"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    step = reference_gpu_step_fn(ref, c, loc, W, bias, device)
+    host = [(x.pin_memory(), t.pin_memory()) for x, t in batches]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    B, D = c["B"], c["D"]
+    h2d = B * D * 2 + int(statistics.mean(t.shape[0] for _, t in batches)) * 8
+
+    def one(i):
+        xh, th = host[i % N_BATCHES]
+        x, t = xh.to(device, non_blocking=True), th.to(device, non_blocking=True)
+        _, loss = step(x, t)
+        return float(loss)                           # the reference's loop reads the loss back every step
+
+    with ClockSampler(0) as clocks:
+        for i in range(args.warmup):
+            one(i)
+        torch.cuda.synchronize(device)
+        times = []
+        for i in range(args.steps):
+            flush.zero_()
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            one(args.warmup + i)
+            torch.cuda.synchronize(device)
+            times.append(time.perf_counter() - t0)
+    ms = statistics.median(times) * 1e3
+    value = B / (ms * 1e-3)
+    config["note"] = ("the reference's three CUDA kernels (legacy wmma code on this GPU) + PyTorch ops for loss, bias gradient and the "
+                      "optimizer pass; host->device copy of the batch and read-back of the loss inside the timed region")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks.summary(),
+            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": "reference",
+                             "sample": f"whole workload, {args.steps} timed steps on GPU 0 (the reference has no CPU implementation; one host thread drives its CUDA kernels)"},
+            "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}}
     print(json.dumps(line), flush=True)
 
 
@@ -392,6 +630,7 @@ def main():
     ap.add_argument("--workload", default="c3")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the extra 2.8M-label measurement")
     ap.add_argument("--aux", action="store_true", help="time the unfused and streaming kernels instead of the train step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

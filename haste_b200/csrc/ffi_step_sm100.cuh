@@ -5,7 +5,7 @@
 // highest-numbered CTAs).  Per group and per 128-row batch tile three UMMA products run out of the same three
 // shared-memory tiles (none is ever transposed or re-gathered; the 128-byte-swizzled "row block" layout serves both
 // operand majors):
-//     X tile [F + 16 rows = slots][128 batch]  rows of xt gathered by TMA (tile::gather4); row F holds ones
+//     X tile [F + 16 rows = slots][128 batch]  rows of xt gathered with cp.async (16 B each); row F holds ones
 //     W tile [G rows = labels][F]               the group's weights, loaded by TMA through a 2-D tensor map
 //     B tile [G rows][16]                       (no swizzle) the group's bias in column 0, zeros elsewhere
 //     Y tile [128 batch][G]                     dLoss/dlogit for the tile, written by the loss-epilogue warps
@@ -15,7 +15,8 @@
 //   backward-weights   dW [l,k] (TMEM, F+16 cols, accumulated over the batch tiles; M = G)
 //                                                = Y^T (MN-major A) * X (K-major B),         K = 128; column F of the
 //                                                  result (the ones row) is the bias gradient
-// Warp roles: warp 0 producer (one elected lane arms the barrier, every lane issues one gather4 per four slots),
+// Warp roles: warp 0 producer (W tile by TMA; X rows by cp.async whose completion arrives on the stage's barrier by
+// itself, so the warp never waits for a copy and keeps several tiles in flight),
 // warp 1 issues forward + backward-features, warp 3 issues backward-weights, 8 loss-epilogue warps turn Z into dY
 // (bf16 rounding of the logit, loss gradient, target bits) and store it swizzled, 4 (F=64) or 8 (F=128) scatter
 // warps drain dXg (TMEM -> registers -> coalesced red.global.add into dxt rows), 8 update warps apply SGD + weight
@@ -33,8 +34,8 @@ namespace haste {
 namespace s100 {
 // out-of-line Philox for the reference random stream: that path is slow anyway and must not bloat the update code
 __device__ __noinline__ static uint32_t rand16_reference_call(uint64_t seed, int64_t flat) { return rand16_reference(seed, flat); }
-// likewise one shared copy of the packed-stream generator and of the bias draw for the update warps
-__device__ __noinline__ static uint4 rand_packed8_call(uint64_t seed, uint32_t step, int64_t row, int col8) { return rand_packed8(seed, step, row, col8); }
+// the packed-stream generator is inlined into the update loop (measured: 4 % of the kernel against a call)
+__device__ __forceinline__ static uint4 rand_packed8_call(uint64_t seed, uint32_t step, int64_t row, int col8) { return rand_packed8(seed, step, row, col8); }
 __device__ __noinline__ static uint32_t rand16_call(uint32_t flags, uint64_t seed, uint32_t step, int64_t row) { return rand16(flags, seed, step, row, 0, 1); }
 
 using namespace sm100;
@@ -61,8 +62,7 @@ struct Cfg {
   static constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
   static constexpr int OFF_BT = OFF_Y + NYS * YSTAGE;
   static constexpr int OFF_LOC = OFF_BT + 2 * BTILE;           // u32 [2][F]: element offset loc * B of each slot's dxt row
-  static constexpr int OFF_LOCR = OFF_LOC + 2 * F * 4;         // int [2][F]: the (clamped) indices themselves, for the gather
-  static constexpr int OFF_YB = OFF_LOCR + 2 * F * 4;          // u32 [2][BT][G/32]: target bits
+  static constexpr int OFF_YB = OFF_LOC + 2 * F * 4;           // u32 [2][BT][G/32]: target bits
   static constexpr int OFF_BAR = OFF_YB + 2 * BT * (G / 32) * 4;
   static constexpr int OFF_MISC = OFF_BAR + 32 * 8;            // tmem base address, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;      // + slack for the 1024-byte alignment of the base
@@ -81,18 +81,23 @@ struct Cfg {
   static_assert(TM_DW + FR <= TM_COLS, "TMEM budget");
 
   static constexpr int N_EA = 8;                      // loss-epilogue warps: 4 TMEM lane quarters x 2 column halves
-  static constexpr int N_EB = 4 * (F / 64);           // scatter warps: 4 TMEM lane quarters x 64-slot chunks
+  static constexpr int EBS = 64;                      // slots per scatter warp
+  static constexpr int N_EB = 4 * (F / EBS);          // scatter warps: 4 TMEM lane quarters x 64-slot chunks
   static constexpr int N_UP = 8;                      // update warps: 4 TMEM lane quarters x 2 slot halves
   static constexpr int W_EA = 4, W_EB = W_EA + N_EA, W_UP = W_EB + N_EB;
-  static constexpr int NTHREADS = (W_UP + N_UP) * 32;
+  static constexpr int NPW = (F == 64) ? 4 : 2;       // producer warps: warp 0, warp 2, then extra warps after the update warps
+  static_assert(NPW >= 1 && NPW <= NXS, "a producer must not run more than one phase ahead on any stage barrier");
+  static constexpr int W_XP = W_UP + N_UP;            // first extra producer warp
+  static constexpr int NTHREADS = (W_XP + (NPW > 2 ? NPW - 2 : 0)) * 32;
   static_assert(NTHREADS <= 1024, "thread budget");
-  static constexpr int EA_COLS = G / 2;               // label columns of a tile handled by one loss-epilogue warp
+  static constexpr int EA_COLS = G * 4 / N_EA;        // label columns of a tile handled by one loss-epilogue warp
   static constexpr int UPS = F / 2;                   // slots updated by one update warp
   static constexpr int ROWS_PER_Q = G / 4;            // label rows of the dW accumulator in one TMEM lane quarter (32, or 16 for M = 64)
 };
 
 struct StepArgs {
   const int32_t* loc;
+  const __nv_bfloat16* xt;
   const int32_t* tgt_ptr;
   const uint32_t* tgt_ent;
   float* dxt;
@@ -135,7 +140,7 @@ __device__ __forceinline__ float tanh_approx(float x) {
 
 template <int G_, int F_, int LOSS, bool WITH_LOSS, bool MOM, bool DEBUG>
 __global__ void __launch_bounds__(Cfg<G_, F_>::NTHREADS, 1)
-ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w) {
+ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CUtensorMap tm_w) {
   using C = Cfg<G_, F_>;
   constexpr int G = C::G, F = C::F, BT = C::BT, FR = C::FR, NXS = C::NXS, NYS = C::NYS, NDX = C::NDX;
   constexpr int XBLK = C::XBLK, XSTAGE = C::XSTAGE, WBLK = C::WBLK, WSTAGE = C::WSTAGE, YBLK = C::YBLK, YSTAGE = C::YSTAGE;
@@ -146,7 +151,6 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(sm);
   uint32_t* loc_s = reinterpret_cast<uint32_t*>(sm + C::OFF_LOC);
-  int* locr_s = reinterpret_cast<int*>(sm + C::OFF_LOCR);
   uint32_t* ybits = reinterpret_cast<uint32_t*>(sm + C::OFF_YB);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::OFF_MISC + 8);
@@ -163,7 +167,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 
   // ---------------- one-time setup
   if (tid == 0) {
-    for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 1); mbar_init(bar(C::B_XEMPTY + i), 1); }
+    for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 32); mbar_init(bar(C::B_XEMPTY + i), 1); }   // X stage: one asynchronous arrival per producer lane
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::B_WFULL + i), 1);  mbar_init(bar(C::B_WEMPTY + i), 1);
       mbar_init(bar(C::B_ZFULL + i), 1);  mbar_init(bar(C::B_ZEMPTY + i), N_EA);
@@ -204,14 +208,18 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
   const int n_my_groups = full_rounds + (cta >= n_cta - rem_groups ? 1 : 0);
   auto group_of = [&](int gi) { return gi < full_rounds ? cta + gi * n_cta : full_rounds * n_cta + (cta - (n_cta - rem_groups)); };
 
-  if (warp == 0) {
-    // ================================================================ producer (TMA)
-    // Per group: the index row (as dxt row offsets for the scatter warps and as plain indices for the gather) and
-    // the bias column go to shared memory with ordinary stores, the W tile comes through the tensor map.  Per batch
-    // tile: F/4 gather4 loads per 64-batch block, each bringing four index rows of xt; lane 0 arms the stage's
-    // barrier with the byte count, then every lane issues its share.
-    int it = 0;                  // X stages armed so far
+  const int prod_id = warp == 0 ? 0 : (warp == 2 ? 1 : (warp >= C::W_XP ? 2 + warp - C::W_XP : -1));
+  if (prod_id >= 0 && prod_id < C::NPW) {
+    // ================================================================ producers
+    // Per group: the index row (as dxt row offsets for the scatter warps) and the bias column go to shared memory
+    // with ordinary stores, the W tile comes through the tensor map.  Per batch tile: F index rows of xt, 256 bytes
+    // each, as 16-byte cp.async copies (two rows per warp instruction) written at their swizzled positions; each
+    // lane then posts an asynchronous arrival that fires when its copies have landed.  (TMA tile::gather4 was
+    // measured for this gather: about 26 cycles per 128-byte row and SM, three times the tile budget.)
+    // The W item of every group belongs to producer 0; the X items (one per batch tile) are dealt round-robin.
+    int it = 0;                  // X items so far (all producers count all of them)
     int w_armed = 0;             // W stages armed so far
+    int my_last = -1;            // last X item this warp actually issued
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = group_of(gi);
       const int ws = gi & 1;
@@ -221,6 +229,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
       int locv[F / 32];
 #pragma unroll
       for (int j = 0; j < F / 32; ++j) locv[j] = min(max(__ldg(lrow + lane + 32 * j), 0), a.D - 1);   // clamped: never addresses outside xt / dxt
+      if (prod_id == 0) {
       uint16_t bv[G / 32];
 #pragma unroll
       for (int j = 0; j < G / 32; ++j) {
@@ -233,7 +242,6 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 #pragma unroll
       for (int j = 0; j < F / 32; ++j) {
         loc_s[ws * F + lane + 32 * j] = static_cast<uint32_t>(locv[j]) * static_cast<uint32_t>(a.B);   // D * B < 2^32 is a launch condition
-        locr_s[ws * F + lane + 32 * j] = locv[j];
       }
 #pragma unroll
       for (int j = 0; j < G / 32; ++j) {
@@ -252,28 +260,37 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
         ++w_armed;
       }
       __syncwarp();
-      for (int t = 0; t < T; ++t) {
+      }
+      for (int t = 0; t < T; ++t, ++it) {
+        if (it % C::NPW != prod_id) continue;
         const int xs = it % NXS;
         const bool okx = mbar_wait(bar(C::B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 2, WL, 100);
         __syncwarp();
         if (!okx || *abort_flag) continue;
         const int b0 = tile_b0(t);
         const uint32_t xb = sbase + C::OFF_X + xs * XSTAGE;
-        if (lane == 0) mbar_arrive_expect_tx(bar(C::B_XFULL + xs), F * 256);
-        __syncwarp();
-        const int4* lr4 = reinterpret_cast<const int4*>(locr_s + ws * F);
+        const int j = lane & 15;                     // 16-byte chunk along the batch: 8 rows each
+        const bool valid = b0 + j * 8 < a.B;
+        const uint32_t dcol = (j >> 3) * XBLK + ((j & 7) << 4);
+        const __nv_bfloat16* src0 = a.xt + b0 + j * 8;
 #pragma unroll
-        for (int i = lane; i < 2 * (F / 4); i += 32) {
-          const int blk = i / (F / 4), r4 = i % (F / 4);
-          const int4 lr = lr4[r4];
-          tma_gather4(xb + blk * XBLK + r4 * 512, &tm_x, b0 + blk * 64, lr.x, lr.y, lr.z, lr.w, bar(C::B_XFULL + xs));
+        for (int jj = 0; jj < F / 32; ++jj) {        // index values jj*32 .. jj*32+31 live in locv[jj] of lane (slot & 31)
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int k = jj * 32 + i * 2 + (lane >> 4);         // slot: two per iteration, 16 lanes each
+            const int lk = __shfl_sync(0xffffffffu, locv[jj], k & 31);
+            cp_async16(xb + ((dcol + k * 128) ^ ((k & 7) << 4)), valid ? src0 + static_cast<int64_t>(lk) * a.B : a.xt, valid);
+          }
         }
-        ++it;
+        cp_async_mbar_arrive_noinc(bar(C::B_XFULL + xs));   // each lane's arrival fires when its copies have landed
+        my_last = it;
       }
     }
     // Every copy this warp started has to land before the CTA may exit (normally the consumers have long seen them;
     // after an abort nobody else waits any more).
-    for (int j = max(0, it - NXS); j < it; ++j) mbar_wait_final(bar(C::B_XFULL + j % NXS), (j / NXS) & 1, WL);
+    // (only the most recent use of each stage: an older phase of the same barrier can no longer be waited for)
+    for (int j = max(0, it - NXS); j < it; ++j)
+      if (j % C::NPW == prod_id && j <= my_last) mbar_wait_final(bar(C::B_XFULL + j % NXS), (j / NXS) & 1, WL);
     for (int j = max(0, w_armed - 2); j < w_armed; ++j) mbar_wait_final(bar(C::B_WFULL + (j & 1)), (j >> 1) & 1, WL);
   } else if (warp == 1 || warp == 3) {
     // ================================================================ MMA issuers (one elected lane each)
@@ -464,19 +481,21 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
         // ragged edge: one warp vote per chunk sends those down a branch with no per-element tests; the rest take
         // the general branch with target bits and a column-valid mask.
 #pragma unroll 1
-        for (int c16 = 0; c16 < EA_COLS; c16 += 16) {
-          uint32_t r[16];
+        constexpr int CH = 16;                             // label columns per TMEM load
+        for (int c16 = 0; c16 < EA_COLS; c16 += CH) {
+          uint32_t r[CH];
           __syncwarp();
-          tmem_ld16(ta + c16, r);
+          tmem_ld(ta + c16, r);
           tmem_ld_wait();
-          const uint32_t ym16 = static_cast<uint32_t>(ym >> c16) & 0xFFFFu;
+          const uint32_t ym16 = static_cast<uint32_t>(ym >> c16) & (CH == 32 ? 0xFFFFFFFFu : 0xFFFFu);
           const bool general = DEBUG || ragged || __any_sync(0xffffffffu, ym16 != 0u);
           uint8_t* yblk = yrow + ((col0 + c16) >> 6) * YBLK;
           const int chunk0 = ((col0 + c16) & 63) >> 3;       // 16-byte chunk inside the 128-byte row of the block
           if (!general) {
             float bce_prod = 1.f;
+            float fl[4] = {0.f, 0.f, 0.f, 0.f};        // partial sums: no serial dependency through one accumulator
 #pragma unroll
-            for (int e8 = 0; e8 < 16; e8 += 8) {
+            for (int e8 = 0; e8 < CH; e8 += 8) {
               uint4 pk;
               float x[8];
               if (LOSS == HASTE_LOSS_SQHINGE) {
@@ -487,7 +506,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   x[i] = fmaf(gs2, round_bf16_as_f32(__uint_as_float(r[e8 + i])), gs2);   // logits are rounded to bf16 first, as the unfused forward stores them
-                  if (WITH_LOSS) { const float m2 = x[i] + fabsf(x[i]); fast_loss = fmaf(m2, m2, fast_loss); }
+                  if (WITH_LOSS) { const float m2 = x[i] + fabsf(x[i]); fl[i & 3] = fmaf(m2, m2, fl[i & 3]); }
                 }
                 pk = make_uint4(pack_bf16x2_relu(x[0], x[1]), pack_bf16x2_relu(x[2], x[3]), pack_bf16x2_relu(x[4], x[5]), pack_bf16x2_relu(x[6], x[7]));
               } else {
@@ -499,17 +518,20 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
                   const float zr = round_bf16_as_f32(__uint_as_float(r[e8 + i]));
                   const float th = tanh_approx(0.5f * zr);
                   x[i] = fmaf(hgs, th, hgs);
-                  if (WITH_LOSS) { tile_loss += zr; tile_loss += fabsf(zr); bce_prod *= fmaf(0.5f, fabsf(th), 0.5f); }
+                  if (WITH_LOSS) { fl[i & 1] += zr; fl[2 + (i & 1)] += fabsf(zr); bce_prod *= fmaf(0.5f, fabsf(th), 0.5f); }
                 }
                 pk = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
               }
               *reinterpret_cast<uint4*>(yblk + (((chunk0 + (e8 >> 3)) ^ (row & 7)) << 4)) = pk;
             }
-            if (LOSS == HASTE_LOSS_BCE && WITH_LOSS) fast_loss += __log2f(bce_prod);
+            if (WITH_LOSS) {
+              if (LOSS == HASTE_LOSS_BCE) { fast_loss += __log2f(bce_prod); tile_loss += (fl[0] + fl[1]) + (fl[2] + fl[3]); }
+              else fast_loss += (fl[0] + fl[1]) + (fl[2] + fl[3]);
+            }
           } else {
             const int nvalid = rows_real - (col0 + c16);           // columns of this chunk that are real labels
 #pragma unroll
-            for (int e8 = 0; e8 < 16; e8 += 8) {
+            for (int e8 = 0; e8 < CH; e8 += 8) {
               float x[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -573,29 +595,29 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
     const int e = warp - C::W_EB;
     const int q = warp & 3;
     const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
-    const int kc = e >> 2;                       // which 64-slot chunk this warp scatters
+    const int kc = e >> 2;                       // which EBS-slot chunk this warp scatters
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int ws = gi & 1;
       mbar_wait(bar(C::B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 12, WL);   // loc_s of this group is in place
-      const uint4* loc4 = reinterpret_cast<const uint4*>(loc_s + ws * F + kc * 64);
+      const uint4* loc4 = reinterpret_cast<const uint4*>(loc_s + ws * F + kc * C::EBS);
       for (int t = 0; t < T; ++t, ++it) {
         const int b0 = tile_b0(t);
         const int ds = it % NDX;
         mbar_wait(bar(C::B_DXFULL + ds), (it / NDX) & 1, abort_flag, a.err, 13, WL);
         tc_fence_after();
-        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DX + ds * F + kc * 64;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DX + ds * F + kc * C::EBS;
         // dXg[b,k] of this thread's batch row goes to dxt[loc[k], b]: for a fixed k the warp's 32 lanes hit 32
         // consecutive floats, so each red below is one 128-byte transaction.  Two halves of 32 slots, so that only
         // 32 accumulator values are live at a time; the stage goes back to the tensor core after the second load.
         const bool do_red = (b0 + row < a.B) && !*abort_flag;
         float* dbase = a.dxt + b0 + row;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < C::EBS / 32; ++half) {
           uint32_t r0[32];
           tmem_ld32(ta + half * 32, r0);
           tmem_ld_wait();
-          if (half == 1) {
+          if (half == C::EBS / 32 - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::B_DXEMPTY + ds));
@@ -615,7 +637,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::B_MEMPTY + ws));    // this warp no longer needs the group's index row
     }
-  } else if (warp >= C::W_UP) {
+  } else if (warp >= C::W_UP && warp < C::W_XP) {
     // ================================================================ update warps: SGD + stochastic rounding
     // Weight / bias update of each finished group from its dW accumulator: warp (q, kh) owns the label rows of TMEM
     // lane quarter q (32 rows for G = 128; 16 for G = 64, where an M = 64 accumulator occupies lanes 0-15 of each
@@ -775,16 +797,15 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
   using C = Cfg<G_, F_>;
   if (int rc = report_pending_status("fused train step")) return rc;
   StepArgs a;
-  a.loc = loc; a.tgt_ptr = tgt_ptr; a.tgt_ent = tgt_ent; a.dxt = dxt; a.loss = loss;
+  a.loc = loc; a.xt = static_cast<const __nv_bfloat16*>(xt); a.tgt_ptr = tgt_ptr; a.tgt_ent = tgt_ent; a.dxt = dxt; a.loss = loss;
   if (int rc = device_status_word(&a.err)) return rc;
   a.B = B; a.L = L; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + G_ - 1) / G_); a.grad_scale = grad_scale;
   a.wait_limit = wait_limit_cycles();
   a.stall_tile = dump ? take_stall_tile() : -1;
   a.z_dump = dump ? static_cast<__nv_bfloat16*>(dump->z) : nullptr; a.ldz = dump ? dump->ldz : 0;
   a.dw_dump = dump ? static_cast<__nv_bfloat16*>(dump->dw) : nullptr; a.db_dump = dump ? static_cast<__nv_bfloat16*>(dump->dbias) : nullptr;
-  CUtensorMap tm_x, tm_w;
-  // xt [D][B]: one box = 64 batch columns of one row (gather4 stacks four rows); W [L][F]: one box = 64 slots x G labels
-  if (int rc = make_tmap_bf16_2d(&tm_x, xt, static_cast<uint64_t>(B), static_cast<uint64_t>(D), static_cast<uint64_t>(B) * 2, 64, 1)) return rc;
+  CUtensorMap tm_w;
+  // W [L][F]: one box = 64 slots x G labels
   if (int rc = make_tmap_bf16_2d(&tm_w, u.w, static_cast<uint64_t>(F_), static_cast<uint64_t>(L), static_cast<uint64_t>(F_) * 2, 64, G_)) return rc;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -798,7 +819,7 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
     auto k = ffi_train_step_sm100_kernel<G_, F_, LK, WLOSS, MOMF, DBG>;                                             \
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);            \
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));         \
-    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_x, tm_w);                                                  \
+    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_w);                                                        \
   }
 #define HASTE_S100_BY_LOSS(WLOSS, MOMF, DBG)                                                                       \
   { if (loss_kind == HASTE_LOSS_BCE) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, WLOSS, MOMF, DBG) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, WLOSS, MOMF, DBG) }

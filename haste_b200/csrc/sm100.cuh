@@ -1,5 +1,4 @@
-// sm_100a primitives in inline PTX: mbarrier with bounded waits, TMA loads (tiled and tile::gather4, never
-// multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
+// sm_100a primitives in inline PTX: mbarrier with bounded waits, tiled TMA loads (never multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
 // zero fill, bulk reduce-add to global.
 #pragma once
 #include <cuda_runtime.h>
@@ -93,19 +92,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
                "l"(tmap), "r"(x), "r"(y), "r"(bar)
                : "memory");
 }
-// Four rows r0..r3 of a 2-D tensor (box = {columns, 1 row}) starting at column x, stacked as four consecutive rows
-// at dst; with a 128-byte box and the 128-byte swizzle each row lands exactly as the UMMA row-block layout wants it.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int x, int r0, int r1, int r2, int r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
-      "l"(tmap), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
-      : "memory");
-}
 
 // ---------------------------------------------------------------- cp.async (16 B, zero fill when !valid)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
   const uint32_t n = valid ? 16u : 0u;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+// Asynchronous arrival: counts as one arrival on `bar` once every cp.async this thread issued before has landed
+// (the barrier's expected count must include it; the pending count is not incremented).  The issuing thread does
+// not wait: it can go on to fill the next stage.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -198,6 +195,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// width chosen by the destination array
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
   uint32_t r;
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(r) : "r"(taddr) : "memory");

@@ -169,10 +169,20 @@ class ShardedFFILayer:
     ``full_*`` tensors describe the whole layer (on any device); each rank copies its slice to ``device``.
     ``group_cost`` (optional, one number per label group, identical on every rank) replaces the split by group
     count with a contiguous split of equal estimated cost; ``group_cost_from_targets`` derives it from a batch.
+
+    Two ways to step:
+      ``step(x, targets)``            kernel, then the all-reduce; returns the summed dX of this step.
+      ``step_pipelined(x, targets, next_batch)``
+                                      three streams: the fused kernel of this step (on ``reserve_sms`` fewer CTAs than
+                                      the GPU has SMs) runs beside the all-reduce of the PREVIOUS step's dX and the
+                                      preparation (transpose, clears, target bucketing) of the NEXT batch.  Returns the
+                                      previous step's summed dX (None on the first call); ``flush()`` returns the last
+                                      one.  Everything enqueued by a call has finished when the caller's stream passes
+                                      the end of the call, so per-call device timing sees all of it.
     """
 
     def __init__(self, full_locations, full_weights, full_bias, group_size, in_features, device, *, process_group=None,
-                 rank=None, world_size=None, group_cost=None, **shard_kwargs):
+                 rank=None, world_size=None, group_cost=None, reserve_sms=8, **shard_kwargs):
         import torch.distributed as dist
         self.dist = dist
         self.pg = process_group
@@ -193,18 +203,99 @@ class ShardedFFILayer:
         self.shard = FusedFFIShard(full_locations[g0:g1].to(device).contiguous(), full_weights[l0:l1].to(device).contiguous(),
                                    None if full_bias is None else full_bias[l0:l1].to(device).contiguous(), group_size,
                                    in_features, label0=l0, **shard_kwargs)
-        self.comm_stream = torch.cuda.Stream(device=device) if (world_size > 1 and torch.device(device).type == "cuda") else None
+        on_gpu = torch.device(device).type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device=device) if (world_size > 1 and on_gpu) else None
+        self.prep_stream = torch.cuda.Stream(device=device) if on_gpu else None
+        self.reserve_sms = int(reserve_sms)
+        self._slots = None          # pipelined path: two sets of per-batch buffers
+        self._cur = 0               # slot of the batch the next step_pipelined call computes on
+        self._staged = False        # slot _cur already holds a prepared batch
+        self._pending = None        # slot whose dX still has to be all-reduced
 
     def step(self, x, targets, want_loss=True):
-        """Returns (dxt summed over all ranks, this rank's loss part).  The all-reduce runs on a side stream;
-        the caller's stream waits for it before returning."""
+        """Returns (dxt summed over all ranks, this rank's loss part): kernel, then the all-reduce, on the caller's
+        stream."""
         dxt, loss = self.shard.step(x, targets, want_loss=want_loss)
-        allreduce_sum(dxt, self.pg, self.comm_stream, self.world)
+        allreduce_sum(dxt, self.pg, None, self.world)
         return dxt, loss
+
+    # ------------------------------------------------------------------ pipelined path
+    def _make_slots(self, B, D, nnz, dev):
+        sh = self.shard
+        self._slots = [dict(xt=torch.empty(D, B, dtype=torch.bfloat16, device=dev), dxt=torch.empty(D, B, dtype=torch.float32, device=dev),
+                            ptr=torch.zeros(sh.NG + 1, dtype=torch.int32, device=dev), ent=torch.zeros(max(1, int(nnz * 1.5)), dtype=torch.int32, device=dev),
+                            loss=torch.zeros(1, dtype=torch.float32, device=dev), prepared=torch.cuda.Event(), computed=torch.cuda.Event(),
+                            reduced=torch.cuda.Event()) for _ in range(2)]
+
+    def _prepare(self, slot, x, targets, stream):
+        sh, b = self.shard, self._slots[slot]
+        if targets.shape[0] > b["ent"].numel():
+            b["ent"] = torch.zeros(int(targets.shape[0] * 1.5) + 1, dtype=torch.int32, device=targets.device)
+        with torch.cuda.stream(stream):
+            _ffi.step_prepare(x, b["xt"], b["dxt"], b["loss"], targets, sh.label0, sh.L, sh.G, b["ptr"], b["ent"])
+            b["prepared"].record(stream)
+
+    def step_pipelined(self, x, targets, next_batch=None, want_loss=True):
+        """One step of the three-stream pipeline (see the class docstring).  ``next_batch``: (x, targets) of the
+        following step, already on the device, or None.  Returns (previous step's summed dxt or None, this step's loss
+        part as a device scalar)."""
+        sh = self.shard
+        dev = x.device
+        cur = torch.cuda.current_stream(dev)
+        B, D = x.shape
+        if self._slots is None or self._slots[0]["xt"].shape != (D, B):
+            self._make_slots(B, D, max(targets.shape[0], 1 if next_batch is None else next_batch[1].shape[0]), dev)
+            if self.world > 1:      # leave SMs free for the collective and the preparation kernels of the other streams
+                _lib.check(_lib.lib.haste_ffi_set_max_ctas(max(1, _sm_count(dev) - self.reserve_sms)), "set_max_ctas")
+        s = self._cur
+        b = self._slots[s]
+        if not self._staged:
+            self._prepare(s, x, targets, cur)                 # first step: nothing was staged before
+        # (1) the previous step's all-reduce, beside this step's kernel
+        prev = self._pending
+        if prev is not None and self.world > 1:
+            pb = self._slots[prev]
+            self.comm_stream.wait_stream(cur)                 # not before this call began (and after the kernel that made it)
+            with torch.cuda.stream(self.comm_stream):
+                self.dist.all_reduce(pb["dxt"], op=self.dist.ReduceOp.SUM, group=self.pg)
+                pb["reduced"].record(self.comm_stream)
+        # (2) the next batch's preparation, beside this step's kernel
+        if next_batch is not None:
+            self.prep_stream.wait_stream(cur)
+            self._prepare(s ^ 1, next_batch[0], next_batch[1], self.prep_stream)
+        # (3) this step's kernel
+        cur.wait_event(b["prepared"])
+        seed, step = sh._keys()
+        flags = _ffi.make_flags(sr=sh.sr, contract=sh.contract, rng=sh.rng, zero_dxt=False, loss=want_loss)
+        _ffi.train_step(sh.loc, b["xt"], sh.w, sh.bias, sh.mom_w, sh.mom_b, b["ptr"], b["ent"], b["dxt"], b["loss"] if want_loss else None,
+                        sh.G, sh.label0, sh.loss_kind, sh.grad_scale, sh.lr, sh.wd, sh.mu, seed, step, flags)
+        sh.steps += 1
+        # everything this call enqueued is done when the caller's stream gets past this point
+        if prev is not None and self.world > 1:
+            cur.wait_event(self._slots[prev]["reduced"])
+        if next_batch is not None:
+            cur.wait_event(self._slots[s ^ 1]["prepared"])
+        out = self._slots[prev]["dxt"] if prev is not None else None
+        self._pending, self._cur, self._staged = s, s ^ 1, next_batch is not None
+        return out, (b["loss"] if want_loss else None)
+
+    def flush(self):
+        """All-reduce the last step's dX (on the caller's stream) and return it."""
+        if self._pending is None:
+            return None
+        dxt = self._slots[self._pending]["dxt"]
+        allreduce_sum(dxt, self.pg, None, self.world)
+        self._pending = None
+        return dxt
+
+
+def _sm_count(device):
+    return torch.cuda.get_device_properties(device).multi_processor_count
 
 
 def allreduce_sum(t, process_group=None, comm_stream=None, world_size=None):
-    """Sum ``t`` over the ranks in place (NCCL for CUDA tensors, any backend for CPU tensors)."""
+    """Sum ``t`` over the ranks in place (NCCL for CUDA tensors, any backend for CPU tensors).  With ``comm_stream`` the
+    collective runs there, after the work already on the current stream, and the current stream waits for it."""
     import torch.distributed as dist
     if world_size is None:
         world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
