@@ -8,8 +8,11 @@ oracle finishes in seconds.  Configuration 5's density (36 positives per row, Zi
 entries into the head group: the shared-memory target bitmap path.
 
 Tolerances: dX rel 1e-2 + abs 1e-3 of its magnitude (bf16 inputs, fp32 accumulation); loss rel 2e-3; updated weights
-and bias: at least 97 % bit-identical to the oracle's and none further than one bf16 step (the products differ from the
-oracle's in the last bits of the fp32 sum, which stochastic rounding turns into an occasional neighbouring bf16 value).
+and bias: at least 97 % bit-identical to the oracle's, and none further from it than one bf16 step of the value plus
+lr x (one bf16 step of its gradient + the gradient's sensitivity to one-step differences in the bf16 loss gradients
+it sums, sum_b step(dY[b,l]) |x[b,k]|): the products differ from the oracle's in the last bits of the fp32 sum and the
+kernel's sigmoid is tanh.approx-based, which the bf16 roundings and stochastic rounding turn into an occasional
+neighbouring bf16 value.
 """
 import numpy as np
 import pytest
@@ -49,13 +52,20 @@ def _step_vs_oracle(name, rng):
     err = (dxt.cpu() - ref["dXt"]).abs()
     assert not (err > 1e-3 * mag + 1e-2 * ref["dXt"].abs()).any(), f"{name}: dX max err {float(err.max())} of {mag}"
     assert abs(float(loss_dev) - ref["loss"]) <= 2e-3 * abs(ref["loss"]), (name, float(loss_dev), ref["loss"])
-    for got, want, what in ((shard.w, ref["W_new"], "weights"), (shard.bias, ref["bias_new"], "bias")):
+    def bf16_step(v):
+        return np.exp2(np.floor(np.log2(np.maximum(np.abs(v), 1e-30))) - 7)
+
+    dy_step = torch.from_numpy(bf16_step(ref["dY"].float().numpy().astype(np.float64))).float()
+    dy_step[ref["dY"].float() == 0] = 0
+    sens_w = fo.backward_weights(inp["loc"], inp["X"].float().abs(), dy_step, G, L, round_bf16=False).numpy().astype(np.float64)
+    sens_b = dy_step.double().sum(0).numpy()
+    for got, want, grad, sens, what in ((shard.w, ref["W_new"], ref["dW"], sens_w, "weights"), (shard.bias, ref["bias_new"], ref["dbias"], sens_b, "bias")):
         gb, wb = fo._bf16_to_bits(got.cpu()), fo._bf16_to_bits(want)
         same = gb == wb
         assert same.mean() >= 0.97, f"{name}: only {same.mean():.4f} of the updated {what} match the oracle bit for bit"
         g, w = px.bf16_bits_to_f32(gb).astype(np.float64), px.bf16_bits_to_f32(wb).astype(np.float64)
-        step = np.exp2(np.floor(np.log2(np.maximum(np.abs(w), 1e-30))) - 7)
-        assert (np.abs(g - w) <= step * 1.0001 + 1e-12)[~same].all(), f"{name}: an updated {what} value is more than one bf16 step off"
+        tol = 1.0001 * (bf16_step(w) + lr * (bf16_step(grad.float().numpy().astype(np.float64)) + sens)) + 1e-12
+        assert (np.abs(g - w) <= tol)[~same].all(), f"{name}: an updated {what} value is further off than a bf16 step of value and gradient"
     # a target-free label far from the head keeps "weight decay only" semantics: its gradient is the loss gradient of
     # negatives, which is what the bulk of the layer sees — covered by the comparison above.  The ragged tail:
     assert shard.w.shape[0] == L
