@@ -176,9 +176,10 @@ class ShardedFFILayer:
                                       three streams: the fused kernel of this step (on ``reserve_sms`` fewer CTAs than
                                       the GPU has SMs) runs beside the all-reduce of the PREVIOUS step's dX and the
                                       preparation (transpose, clears, target bucketing) of the NEXT batch.  Returns the
-                                      previous step's summed dX (None on the first call); ``flush()`` returns the last
-                                      one.  Everything enqueued by a call has finished when the caller's stream passes
-                                      the end of the call, so per-call device timing sees all of it.
+                                      previous step's summed dX (None on the first call; valid until the next call,
+                                      which reuses its buffer); ``flush()`` returns the last one.  Everything enqueued
+                                      by a call has finished when the caller's stream passes the end of the call, so
+                                      per-call device timing sees all of it.
     """
 
     def __init__(self, full_locations, full_weights, full_bias, group_size, in_features, device, *, process_group=None,
@@ -207,7 +208,7 @@ class ShardedFFILayer:
         self.comm_stream = torch.cuda.Stream(device=device) if (world_size > 1 and on_gpu) else None
         self.prep_stream = torch.cuda.Stream(device=device) if on_gpu else None
         self.reserve_sms = int(reserve_sms)
-        self._slots = None          # pipelined path: two sets of per-batch buffers
+        self._slots = None          # pipelined path: three sets of per-batch buffers (being reduced / computed / prepared)
         self._cur = 0               # slot of the batch the next step_pipelined call computes on
         self._staged = False        # slot _cur already holds a prepared batch
         self._pending = None        # slot whose dX still has to be all-reduced
@@ -225,7 +226,7 @@ class ShardedFFILayer:
         self._slots = [dict(xt=torch.empty(D, B, dtype=torch.bfloat16, device=dev), dxt=torch.empty(D, B, dtype=torch.float32, device=dev),
                             ptr=torch.zeros(sh.NG + 1, dtype=torch.int32, device=dev), ent=torch.zeros(max(1, int(nnz * 1.5)), dtype=torch.int32, device=dev),
                             loss=torch.zeros(1, dtype=torch.float32, device=dev), prepared=torch.cuda.Event(), computed=torch.cuda.Event(),
-                            reduced=torch.cuda.Event()) for _ in range(2)]
+                            reduced=torch.cuda.Event()) for _ in range(3)]
 
     def _prepare(self, slot, x, targets, stream):
         sh, b = self.shard, self._slots[slot]
@@ -248,6 +249,7 @@ class ShardedFFILayer:
             if self.world > 1:      # leave SMs free for the collective and the preparation kernels of the other streams
                 _lib.check(_lib.lib.haste_ffi_set_max_ctas(max(1, _sm_count(dev) - self.reserve_sms)), "set_max_ctas")
         s = self._cur
+        nxt = (s + 1) % 3           # the previous step's slot is (s + 2) % 3: three distinct buffers are live per call
         b = self._slots[s]
         if not self._staged:
             self._prepare(s, x, targets, cur)                 # first step: nothing was staged before
@@ -262,7 +264,7 @@ class ShardedFFILayer:
         # (2) the next batch's preparation, beside this step's kernel
         if next_batch is not None:
             self.prep_stream.wait_stream(cur)
-            self._prepare(s ^ 1, next_batch[0], next_batch[1], self.prep_stream)
+            self._prepare(nxt, next_batch[0], next_batch[1], self.prep_stream)
         # (3) this step's kernel
         cur.wait_event(b["prepared"])
         seed, step = sh._keys()
@@ -274,9 +276,9 @@ class ShardedFFILayer:
         if prev is not None and self.world > 1:
             cur.wait_event(self._slots[prev]["reduced"])
         if next_batch is not None:
-            cur.wait_event(self._slots[s ^ 1]["prepared"])
+            cur.wait_event(self._slots[nxt]["prepared"])
         out = self._slots[prev]["dxt"] if prev is not None else None
-        self._pending, self._cur, self._staged = s, s ^ 1, next_batch is not None
+        self._pending, self._cur, self._staged = s, nxt, next_batch is not None
         return out, (b["loss"] if want_loss else None)
 
     def flush(self):
