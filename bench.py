@@ -615,11 +615,59 @@ def run_aux(args):
         ("rewire layer-wide fraction 0.15, max score, unused regrow, zero init, regroup",
          lambda: hffi.rewire_ex(w2, loc, None, D, G, 0, 1, 2, 0.0, int(NG * F * 0.15), 1, 0, True, SEED, 1, None, rw_scratch), 6 * L * F + 8 * NG * F + 12 * NG * F),
     ]
+    rows += probe_rows(c, xt, dev, peaks, timeit)
     for name, fn, nbytes in rows:
+        if nbytes is None:                                   # a probe that prints its own line
+            fn()
+            continue
         ms = timeit(fn)
         gbs = nbytes / (ms * 1e-3) / 1e9
         print(json.dumps({"kernel": name, "workload": args.workload, "ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs,
                           "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "bound": "hbm"}), flush=True)
+
+
+def probe_rows(c, xt, dev, peaks, timeit):
+    """Rate probes of the fused step's three resources at the workload's sizes (haste_probe_* entry points): the dX
+    scatter as reduce-adds into dxt, the X gather (TMA gather4 against cp.async), and the tcgen05.mma issue rate."""
+    from haste_b200 import _lib
+    lib, check = _lib.lib, _lib.check
+    B, D = c["B"], c["D"]
+    if B % 128 != 0 or D < 128:
+        return []
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    st = lambda: torch.cuda.current_stream(dev).cuda_stream
+    dxt = torch.zeros(D, B, dtype=torch.float32, device=dev)
+    tiles = 140                                              # 148 SMs x 140 tiles x 32 KB = 679 MB: one C3 step's scatter
+    rows = []
+
+    def emit(name, ms, unit_bytes, extra):
+        gbs = unit_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps(dict(kernel=name, workload="probe", ms=ms, algorithmic_bytes=unit_bytes, **{"GB/s": gbs}, **extra)), flush=True)
+
+    for mode, what in ((0, "scalar red, 128 B per warp instruction (the step's pattern)"), (1, "red.v4 along one row, 512 B per warp instruction"),
+                       (2, "red.v4 across 32 rows, 16 B each (a transposed accumulator's pattern)")):
+        def run(mode=mode, what=what):
+            ms = timeit(lambda: check(lib.haste_probe_red_rate(dxt.data_ptr(), D, B, mode, tiles, st()), "probe"))
+            emit(f"probe: dX scatter alone, {what}", ms, sms * tiles * 32768, {"bound": "l2 reduce-add"})
+        rows.append((what, run, None))
+    for mode, what in ((0, "TMA tile::gather4"), (1, "cp.async, 1 warp"), (2, "cp.async, 2 warps"), (4, "cp.async, 4 warps")):
+        def run(mode=mode, what=what):
+            ms = timeit(lambda: check(lib.haste_probe_gather_rate(xt.data_ptr(), D, B, mode, tiles, st()), "probe"))
+            cyc = ms * 1e-3 * 1.965e9 / tiles
+            emit(f"probe: X gather alone (64 rows x 256 B per tile), {what}", ms, sms * tiles * 16384,
+                 {"bound": "l2 -> smem", "cycles_per_tile_at_1965MHz": cyc})
+        rows.append((what, run, None))
+    cyc = torch.zeros(2, dtype=torch.int64, device=dev)
+    for N, amn, bmn, what in ((128, 1, 0, "forward: A MN-major, B K-major, N=128"), (64, 0, 1, "backward-features: A K-major, B MN-major, N=64"),
+                              (80, 1, 0, "backward-weights: A MN-major, B K-major, N=80"), (144, 1, 0, "backward-weights at F=128: N=144")):
+        def run(N=N, amn=amn, bmn=bmn, what=what):
+            check(lib.haste_probe_umma_rate(N, amn, bmn, 64, cyc.data_ptr(), st()), "probe")
+            torch.cuda.synchronize()
+            n = 64 * 8
+            print(json.dumps(dict(kernel=f"probe: tcgen05.mma M=128 K=16, {what}", workload="probe", issue_cycles_per_mma=float(cyc[0]) / n,
+                                  complete_cycles_per_mma=float(cyc[1]) / n, ideal_cycles_per_mma=128.0 * N * 16 / 4096.0)), flush=True)
+        rows.append((what, run, None))
+    return rows
 
 
 def main():

@@ -22,6 +22,7 @@ P, I64, F32, U64, U32, I32 = c_void_p, c_int64, c_float, c_uint64, c_uint32, c_i
 # name -> argtypes, in the order of include/haste_ffi.h
 SIGNATURES = {
     "haste_ffi_forward": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, P],
+    "haste_ffi_forward_into": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, P],
     "haste_ffi_backward_features": [P, P, P, P, I64, I64, I64, I64, I64, I64, U32, P],
     "haste_ffi_backward_weights": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, P],
     "haste_ffi_backward": [P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, U32, P],
@@ -47,6 +48,9 @@ SIGNATURES = {
     "haste_poll_status": [],
     "haste_debug_set_wait_limit": [c_longlong],
     "haste_debug_stall_next_step": [I32],
+    "haste_probe_red_rate": [P, I64, I64, I32, I32, P],
+    "haste_probe_gather_rate": [P, I64, I64, I32, I32, P],
+    "haste_probe_umma_rate": [I32, I32, I32, I32, P, P],
 }
 
 for _name, _args in SIGNATURES.items():

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libhaste_ffi.so")
-SOURCES = ["api.cu", "runtime.cu", "ffi_mma.cu", "ffi_step_sm100_g128.cu", "ffi_step_sm100_g64.cu", "ffi_forward_sm100.cu", "ffi_backward_sm100.cu", "elementwise.cu", "rewire.cu", "topk.cu"]
+SOURCES = ["api.cu", "runtime.cu", "ffi_mma.cu", "ffi_step_sm100_g128.cu", "ffi_step_sm100_g64.cu", "ffi_forward_sm100.cu", "ffi_backward_sm100.cu", "elementwise.cu", "rewire.cu", "topk.cu", "probes.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

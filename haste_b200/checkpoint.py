@@ -29,12 +29,21 @@ def find_key_end(state_dict, suffix):
 
 
 def layer_tensors(state_dict, prefix):
-    """(group_locations, weights, bias-or-None) of the FFI layer stored under ``prefix`` (e.g. 'tail_layer.')."""
-    gk, wk = find_key_end(state_dict, prefix + "group_locations"), find_key_end(state_dict, prefix + "weights")
-    if gk is None or wk is None:
-        raise KeyError(f"{prefix}group_locations / {prefix}weights not found in the state dict")
-    bk = find_key_end(state_dict, prefix + "bias")
-    return state_dict[gk], state_dict[wk], (state_dict[bk] if bk is not None else None)
+    """(group_locations, weights, bias-or-None) of the FFI layer stored under ``prefix`` (e.g. 'tail_layer.').
+
+    The three entries must belong to the same module: the module path is taken from the ``group_locations`` key
+    (only FFI layers have that buffer), and ``weights`` / ``bias`` are looked up under exactly that path — a suffix
+    search for 'bias' alone could pick an encoder's bias.  With an empty ``prefix`` the state dict must hold exactly
+    one FFI layer."""
+    cands = [k for k in state_dict.keys() if k == prefix + "group_locations" or (k.endswith("." + prefix + "group_locations") if prefix else k.endswith("group_locations"))]
+    if len(cands) != 1:
+        raise KeyError(f"expected exactly one '{prefix}group_locations' entry in the state dict, found {len(cands)}: {cands[:4]}")
+    gk = cands[0]
+    base = gk[:-len("group_locations")]
+    wk, bk = base + "weights", base + "bias"
+    if wk not in state_dict:
+        raise KeyError(f"{wk} not found in the state dict")
+    return state_dict[gk], state_dict[wk], state_dict.get(bk)
 
 
 def shard_bounds(L, group_size, world_size, group_cost=None):

@@ -79,7 +79,17 @@ int haste_ffi_forward(const int32_t* loc, const void* xt, const void* w, const v
   REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who);
   if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
   if (ldz < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldz=%lld < L=%lld", who, (long long)ldz, (long long)L);
-  return launch_forward(loc, xt, w, bias, z, B, D, F, L, G, ldz, static_cast<cudaStream_t>(stream));
+  return launch_forward(loc, xt, w, bias, z, B, D, F, L, G, ldz, ldz, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_forward_into(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
+                           int64_t L, int64_t G, int64_t ldz, int64_t zcols, haste_stream_t stream) {
+  const char* who = "haste_ffi_forward_into";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(z, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (zcols < L || ldz < zcols) return fail(HASTE_ERR_BAD_ARG, "%s: need L <= zcols <= ldz (L=%lld zcols=%lld ldz=%lld)", who, (long long)L, (long long)zcols, (long long)ldz);
+  return launch_forward(loc, xt, w, bias, z, B, D, F, L, G, ldz, zcols, static_cast<cudaStream_t>(stream));
 }
 
 int haste_ffi_backward_features(const void* w, const int32_t* loc, const void* dy, float* dxt, int64_t B, int64_t D, int64_t F, int64_t L,

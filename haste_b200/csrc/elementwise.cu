@@ -2,6 +2,8 @@
 // stand-alone gradient tensor, the dX transpose+round tail, the bf16 transpose of the features and the
 // COO target bucketing.  All are HBM-bound: 16-byte accesses, grid sized to a multiple of the SM count.
 #include "common.cuh"
+
+#include <mutex>
 #include "launchers.h"
 
 namespace haste {
@@ -350,10 +352,13 @@ constexpr int64_t NOALLOC_MAX_GROUPS = 65536;
 static __device__ __align__(256) int32_t g_bucket_scratch[NOALLOC_MAX_GROUPS];
 
 // In host code `g_bucket_scratch` is only a handle for the device symbol, not a device address, so the address
-// is looked up once per device (with that device current) and cached.
+// is looked up once per device (with that device current) and cached.  The cache is guarded by a mutex: host
+// threads may make their first call on a device at the same time.
 static int32_t* noalloc_scratch_ptr(int* rc) {
   constexpr int MAX_DEV = 64;
   static int32_t* cache[MAX_DEV] = {nullptr};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) {

@@ -14,6 +14,7 @@
 // the dW accumulator into bf16 rows of dw / dbias at the end of each group.  Requires 16-byte-aligned dY rows (ldy % 8 == 0).
 #include "common.cuh"
 #include "launchers.h"
+#include "runtime.h"
 #include "sm100.cuh"
 
 namespace haste {
@@ -326,18 +327,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
   if (warp == 1) tmem_dealloc(tmem, TM_COLS);
 }
 
-static int* g_err_host = nullptr;
-static int* g_err_dev = nullptr;
-static int ensure_err_flag() {
-  if (g_err_host != nullptr) return HASTE_OK;
-  cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&g_err_host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
-  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaHostAlloc(error flag): %s", cudaGetErrorString(e));
-  *g_err_host = 0;
-  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_err_dev), g_err_host, 0);
-  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaHostGetDevicePointer: %s", cudaGetErrorString(e));
-  return HASTE_OK;
-}
-
 }  // namespace b100
 
 bool backward_sm100_supported(const void* dy, const void* dw, int64_t B, int64_t F, int64_t G, int64_t ldy) {
@@ -347,16 +336,13 @@ bool backward_sm100_supported(const void* dy, const void* dw, int64_t B, int64_t
 int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
                           int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st) {
   using namespace b100;
-  if (int rc = ensure_err_flag()) return rc;
-  if (*g_err_host != 0) {
-    const int code = *g_err_host;
-    *g_err_host = 0;
-    return fail(HASTE_ERR_TIMEOUT, "an earlier tcgen05 backward gave up waiting on an on-chip barrier (wait id %d); its outputs are invalid", code);
-  }
+  if (int rc = report_pending_status("tcgen05 backward")) return rc;
+  int* err_dev = nullptr;
+  if (int rc = device_status_word(&err_dev)) return rc;
   BwdArgs a;
   a.loc = loc; a.xt = static_cast<const __nv_bfloat16*>(xt); a.w = static_cast<const __nv_bfloat16*>(w);
   a.dy = static_cast<const __nv_bfloat16*>(dy); a.dxt = dxt; a.dw = static_cast<__nv_bfloat16*>(dw);
-  a.dbias = static_cast<__nv_bfloat16*>(dbias); a.err = g_err_dev;
+  a.dbias = static_cast<__nv_bfloat16*>(dbias); a.err = err_dev;
   a.B = B; a.L = L; a.ldy = ldy; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + G - 1) / G);
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

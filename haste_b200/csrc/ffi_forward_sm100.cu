@@ -11,6 +11,7 @@
 // covers whole 256-byte row segments of z.  All waits are bounded (see mbar_wait).
 #include "common.cuh"
 #include "launchers.h"
+#include "runtime.h"
 #include "sm100.cuh"
 
 namespace haste {
@@ -48,7 +49,7 @@ struct FwdArgs {
   const __nv_bfloat16* bias;
   __nv_bfloat16* z;
   int* err;
-  int64_t B, L, ldz;
+  int64_t B, L, ldz, zw;   // zw: writable width of a row of z (columns L..zw-1 receive zeros)
   int D, NG;
 };
 
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
       const int g = blockIdx.x + gi * gridDim.x;
       const int ws = gi & 1;
       const int64_t l0 = static_cast<int64_t>(g) * G;
-      const int cvalid = static_cast<int>(imin64(G, a.ldz - l0));      // columns of this group that exist in z (zeros past L)
+      const int cvalid = static_cast<int>(imin64(G, a.zw - l0));      // columns of this group that exist in z (zeros past L)
       mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 26, WAIT_LIMIT);    // bias row in place
       const float4* bs4 = reinterpret_cast<const float4*>(bias_s + ws * G + h * 64);
       for (int t = 0; t < T; ++t, ++it) {
@@ -265,18 +266,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_forward_sm100_kernel(FwdArgs 
   if (warp == 1) tmem_dealloc(tmem, TM_COLS);
 }
 
-static int* g_err_host = nullptr;
-static int* g_err_dev = nullptr;
-static int ensure_err_flag() {
-  if (g_err_host != nullptr) return HASTE_OK;
-  cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&g_err_host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
-  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaHostAlloc(error flag): %s", cudaGetErrorString(e));
-  *g_err_host = 0;
-  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_err_dev), g_err_host, 0);
-  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaHostGetDevicePointer: %s", cudaGetErrorString(e));
-  return HASTE_OK;
-}
-
 }  // namespace f100
 
 bool forward_sm100_supported(const void* z, int64_t B, int64_t F, int64_t G, int64_t ldz) {
@@ -284,18 +273,15 @@ bool forward_sm100_supported(const void* z, int64_t B, int64_t F, int64_t G, int
 }
 
 int launch_forward_sm100(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
-                         int64_t L, int64_t G, int64_t ldz, cudaStream_t st) {
+                         int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st) {
   using namespace f100;
-  if (int rc = ensure_err_flag()) return rc;
-  if (*g_err_host != 0) {
-    const int code = *g_err_host;
-    *g_err_host = 0;
-    return fail(HASTE_ERR_TIMEOUT, "an earlier tcgen05 forward gave up waiting on an on-chip barrier (wait id %d); its output is invalid", code);
-  }
+  if (int rc = report_pending_status("tcgen05 forward")) return rc;
+  int* err_dev = nullptr;
+  if (int rc = device_status_word(&err_dev)) return rc;
   FwdArgs a;
   a.loc = loc; a.xt = static_cast<const __nv_bfloat16*>(xt); a.w = static_cast<const __nv_bfloat16*>(w);
-  a.bias = static_cast<const __nv_bfloat16*>(bias); a.z = static_cast<__nv_bfloat16*>(z); a.err = g_err_dev;
-  a.B = B; a.L = L; a.ldz = ldz; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + G - 1) / G);
+  a.bias = static_cast<const __nv_bfloat16*>(bias); a.z = static_cast<__nv_bfloat16*>(z); a.err = err_dev;
+  a.B = B; a.L = L; a.ldz = ldz; a.zw = zw; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + G - 1) / G);
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

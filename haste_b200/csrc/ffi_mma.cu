@@ -130,7 +130,7 @@ template <int G>
 __global__ void __launch_bounds__(NT) ffi_forward_kernel(const int32_t* __restrict__ loc, const __nv_bfloat16* __restrict__ xt,
                                                          const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
                                                          __nv_bfloat16* __restrict__ z, int64_t B, int D, int F, int64_t L,
-                                                         int64_t ldz) {
+                                                         int64_t ldz, int64_t zw) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = blockIdx.x;
@@ -167,8 +167,8 @@ __global__ void __launch_bounds__(NT) ffi_forward_kernel(const int32_t* __restri
     *reinterpret_cast<__nv_bfloat162*>(Cs + (m0 + qr + 8) * ldc + c) = __floats2bfloat162_rn(acc[0][ni][2] + b0v, acc[0][ni][3] + b1v);
   }
   __syncthreads();
-  // coalesced store of the [BT][G] tile; columns up to ldz are written (zeros past L)
-  const int cvalid = static_cast<int>(imin64(G, ldz - l0));
+  // coalesced store of the [BT][G] tile; columns up to zw (the writable width of a row) are written (zeros past L)
+  const int cvalid = static_cast<int>(imin64(G, zw - l0));
   const int bvalid = static_cast<int>(imin64(BT, B - b0));
   constexpr int CH = G / 8;
   for (int idx = tid; idx < BT * CH; idx += NT) {
@@ -511,11 +511,9 @@ static int set_smem(K kernel, size_t bytes) {
   else { constexpr int F_ = 128; __VA_ARGS__; }
 
 int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
-                   int64_t L, int64_t G, int64_t ldz, cudaStream_t st) {
+                   int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st) {
   // Shape dispatch: the tcgen05 kernel where its tile shapes apply, the warp-mma kernel otherwise
-  // (HASTE_FWD_IMPL=mma in the environment forces the latter, to compare the two on the same inputs).
-  static const bool force_mma = [] { const char* e = getenv("HASTE_FWD_IMPL"); return e != nullptr && strcmp(e, "mma") == 0; }();
-  if (!force_mma && forward_sm100_supported(z, B, F, G, ldz)) return launch_forward_sm100(loc, xt, w, bias, z, B, D, F, L, G, ldz, st);
+  if (forward_sm100_supported(z, B, F, G, ldz)) return launch_forward_sm100(loc, xt, w, bias, z, B, D, F, L, G, ldz, zw, st);
   const int64_t NG = (L + G - 1) / G;
   dim3 grid(static_cast<unsigned>(NG), static_cast<unsigned>((B + BT - 1) / BT));
   const size_t sm = fwd_smem(int(G), int(F));
@@ -523,7 +521,7 @@ int launch_forward(const int32_t* loc, const void* xt, const void* w, const void
     auto k = ffi_forward_kernel<G_>;
     if (int rc = set_smem(k, sm)) return rc;
     k<<<grid, NT, sm, st>>>(loc, (const __nv_bfloat16*)xt, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)z, B,
-                            int(D), int(F), L, ldz);
+                            int(D), int(F), L, ldz, zw);
   });
   return check_launch("ffi_forward_kernel");
 }

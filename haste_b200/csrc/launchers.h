@@ -18,11 +18,12 @@ struct UpdateArgs {
   int64_t label0;   // global index of the shard's first label (random-bit counters are global)
 };
 
+// zw: writable width of a row of z, L <= zw <= ldz (columns L..zw-1 receive zeros)
 int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
-                   int64_t L, int64_t G, int64_t ldz, cudaStream_t st);
+                   int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st);
 bool forward_sm100_supported(const void* z, int64_t B, int64_t F, int64_t G, int64_t ldz);
 int launch_forward_sm100(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
-                         int64_t L, int64_t G, int64_t ldz, cudaStream_t st);
+                         int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st);
 int launch_bwd_features(const void* w, const int32_t* loc, const void* dy, float* dxt, int64_t B, int64_t D, int64_t F, int64_t L,
                         int64_t G, int64_t ldy, cudaStream_t st);
 int launch_bwd_weights(const void* xt, const int32_t* loc, const void* dy, void* dw, void* dbias, const UpdateArgs* upd, int64_t B,

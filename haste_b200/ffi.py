@@ -17,7 +17,9 @@ def _req(t, name, dtype=None, contiguous=True):
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor (this library has no CPU path)")
     if dtype is not None and t.dtype != dtype:
-        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+        hint = (" (the kernels compute in bf16 with fp32 accumulation only: create the layer's parameters with "
+                "dtype=torch.bfloat16 / run it under amp.dtype=bfloat16)") if dtype == torch.bfloat16 else ""
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}{hint}")
     if contiguous and not t.is_contiguous():
         raise RuntimeError(f"{name} must be contiguous")
     return t
@@ -56,6 +58,23 @@ def forward(loc, xt, w, bias, G):
         check(lib.haste_ffi_forward(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), _ptr(z), B, D, F, L, G, ldz, _stream(xt)),
               "ffi_forward")
     return z.narrow(1, 0, L)
+
+
+def forward_into(loc, xt, w, bias, G, out, col0):
+    """Write the logits into columns col0 .. col0+L-1 of ``out`` (bf16 [B, ld], row stride ld): no intermediate
+    tensor, no concatenation.  Nothing outside that column block is written."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    _req(out, "out", torch.bfloat16, contiguous=False)
+    if bias is not None:
+        _req(bias, "bias", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    if out.dim() != 2 or out.shape[0] != B or out.stride(1) != 1 or col0 < 0 or col0 + L > out.shape[1]:
+        raise RuntimeError(f"out must be [B={B}, >= {col0 + L}] with unit column stride")
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_forward_into(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), out.data_ptr() + 2 * col0, B, D, F, L, G,
+                                         out.stride(0), L, _stream(xt)), "ffi_forward_into")
+    return out
 
 
 def _rows(dy, L):

@@ -21,7 +21,8 @@ class GroupFixedFanIn(torch.nn.Module):
 
     Constructor arguments are the reference's.  Keyword-only additions: ``regrow`` ('replace' = uniform with
     replacement as in the reference; 'unused' = only indices the row does not hold yet), ``regroup`` (sort
-    every index row after rewiring and permute the weight columns with it), ``seed`` for the Philox draws,
+    every index row after rewiring and permute the weight columns with it), ``seed`` for the Philox draws (None,
+    the default, derives one from the layer's shape, so that two different layers do not draw the same indices),
     ``score_mode`` ('mean' or 'max' of |w| over a group's rows) and ``prune_scope`` ('group': the fraction is
     taken inside every group, as shared_ffi/rewire.py does; 'global': over all (group, slot) pairs of the layer,
     as src/group_fanin_real.py:232-250 does).
@@ -30,7 +31,7 @@ class GroupFixedFanIn(torch.nn.Module):
 
     def __init__(self, in_features: int, out_features: int, fan_in: int, bias: bool = True, device=None, dtype=None, *,
                  group_size=32, prune_mode="threshold", rewire_threshold=None, rewire_fraction=None, growth_mode="random",
-                 init_mode="random", regrow="replace", regroup=False, seed=0, score_mode="mean", prune_scope="group", **kwargs):
+                 init_mode="random", regrow="replace", regroup=False, seed=None, score_mode="mean", prune_scope="group", **kwargs):
         super().__init__(**kwargs)
         factory_kwargs = {'device': device, 'dtype': dtype}
         self.in_features, self.out_features, self.fan_in = in_features, out_features, fan_in
@@ -45,6 +46,8 @@ class GroupFixedFanIn(torch.nn.Module):
         elif prune_mode == "fraction" and rewire_fraction is None:
             raise ValueError("rewire_fraction must be specified for prune_mode 'fraction'")
         self.prune_mode, self.growth_mode, self.init_mode = prune_mode, growth_mode, init_mode
+        if seed is None:
+            seed = (in_features * 1000003 + out_features * 10007 + fan_in * 101 + group_size) & 0x7FFFFFFF
         self.regrow, self.regroup, self.seed = regrow, bool(regroup), int(seed)
         self.score_mode, self.prune_scope = score_mode, prune_scope
         self._rewire_calls = 0
@@ -72,6 +75,23 @@ class GroupFixedFanIn(torch.nn.Module):
 
     def forward(self, features):
         return ops.group_ffi_mul(features, self.weights, self.group_locations, self.bias, gsize=self.group_size)
+
+    # The position in the rewiring random stream (seed, number of rewire calls so far) travels with the state dict,
+    # so that a resumed run continues the stream instead of replaying the draws of the first rewire.  State dicts
+    # written by the reference have no such entry; loading them keeps the constructor's values.
+    def get_extra_state(self):
+        return {"rewire_seed": int(self.seed), "rewire_calls": int(self._rewire_calls)}
+
+    def set_extra_state(self, state):
+        if state:
+            self.seed = int(state.get("rewire_seed", self.seed))
+            self._rewire_calls = int(state.get("rewire_calls", self._rewire_calls))
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+        extra = prefix + "_extra_state"
+        if extra in missing_keys:          # a reference checkpoint: nothing to restore, not an error
+            missing_keys.remove(extra)
 
     def extra_repr(self) -> str:
         return 'in_features={}, out_features={}, fan_in={}, bias={}'.format(

@@ -65,6 +65,14 @@ int haste_ffi_forward(const int32_t* loc, const void* xt, const void* w, const v
                       int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldz,
                       haste_stream_t stream);
 
+/* The same forward writing into a block of columns of a wider matrix: z points at the block's first column of
+ * row 0, ldz is the wider matrix's row stride, and only columns 0..zcols-1 of each row (relative to z) are written —
+ * L logits, zeros in L..zcols-1.  With it the sparse tail's logits land next to a dense head's in one [B, L_head +
+ * L_tail] buffer, where the reference concatenates two tensors (src/model.py:245-248). */
+int haste_ffi_forward_into(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z,
+                           int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldz, int64_t zcols,
+                           haste_stream_t stream);
+
 /* Backward w.r.t. features: dxt[loc[g,k], b] += sum_{l in g} w[l,k] * dy[b,l]  (fp32 atomics).
  * flags: HASTE_F_ZERO_DXT clears dxt first (the reference allocates zeros).
  * Replaces ffi_backward_features_cuda (shared_ffi/ffi_backward_features.cu:417-633). */
@@ -133,7 +141,8 @@ int haste_ffi_step_prepare(const void* x, void* xt, float* dxt, float* loss, con
  * Same inputs, outputs and result as haste_targets_bucket.  Limits and rules:
  *   - at most 65536 label groups (ceil(L/G)); more returns HASTE_ERR_TOO_LARGE — use haste_targets_bucket then;
  *   - the first call on each device looks up the array's device address (the device must be current, as for
- *     every call); make that first call before starting any stream capture;
+ *     every call; the lookup is serialised between host threads); make that first call before starting any
+ *     stream capture;
  *   - all calls on a device share the one array: two calls that may overlap on the GPU (different streams)
  *     race — order them.  The array keeps the last call's contents; each call clears the part it uses itself;
  *   - calls no cudaMalloc / cudaFree nor any allocating library routine. */
@@ -256,6 +265,20 @@ int haste_ffi_step(const void* x, const int32_t* coo, int64_t nnz, const int32_t
  * 1 <= k <= 128. */
 int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int32_t k,
                       float* vals, int32_t* idx, haste_stream_t stream);
+
+/* Rate probes (measurement only; timed by the benchmark's auxiliary mode; no counterpart in the reference).  Each
+ * isolates one access pattern of the fused train step at the step's own sizes:
+ *   haste_probe_red_rate     fp32 reduce-add of `tiles_per_cta` tiles of 64 rows x 128 floats per SM into dxt [D,B]
+ *                            (B % 128 == 0): mode 0 scalar red, one 128-byte transaction per warp instruction (what the
+ *                            step issues); 1 red.v4 along one row; 2 red.v4 across 32 rows per warp instruction
+ *   haste_probe_gather_rate  gathering `tiles_per_cta` tiles of 64 rows x 256 B of xt [D,B] (bf16) per SM into
+ *                            swizzled shared memory: mode 0 TMA tile::gather4; 1, 2, 4 = cp.async from that many warps
+ *   haste_probe_umma_rate    8 * iters back-to-back tcgen05.mma (M=128, K=16, given N and operand majors) on one SM;
+ *                            cycles_out (device, 2 x int64) receives the cycles to issue them and to complete them */
+int haste_probe_red_rate(float* dxt, int64_t D, int64_t B, int32_t mode, int32_t tiles_per_cta, haste_stream_t stream);
+int haste_probe_gather_rate(const void* xt, int64_t D, int64_t B, int32_t mode, int32_t tiles_per_cta, haste_stream_t stream);
+int haste_probe_umma_rate(int32_t N, int32_t a_mn_major, int32_t b_mn_major, int32_t iters, long long* cycles_out,
+                          haste_stream_t stream);
 
 /* Debug check: every loc value in [0,D).  Synchronises the stream. */
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream);
