@@ -650,7 +650,8 @@ def probe_rows(c, xt, dev, peaks, timeit):
             ms = timeit(lambda: check(lib.haste_probe_red_rate(dxt.data_ptr(), D, B, mode, tiles, st()), "probe"))
             emit(f"probe: dX scatter alone, {what}", ms, sms * tiles * 32768, {"bound": "l2 reduce-add"})
         rows.append((what, run, None))
-    for mode, what in ((0, "TMA tile::gather4"), (1, "cp.async, 1 warp"), (2, "cp.async, 2 warps"), (4, "cp.async, 4 warps")):
+    for mode, what in ((0, "TMA tile::gather4, 1 issuing warp"), (12, "TMA tile::gather4, 2 issuing warps"), (14, "TMA tile::gather4, 4 issuing warps"),
+                       (1, "cp.async, 1 warp"), (2, "cp.async, 2 warps"), (4, "cp.async, 4 warps")):
         def run(mode=mode, what=what):
             ms = timeit(lambda: check(lib.haste_probe_gather_rate(xt.data_ptr(), D, B, mode, tiles, st()), "probe"))
             cyc = ms * 1e-3 * 1.965e9 / tiles

@@ -41,6 +41,10 @@ SIGNATURES = {
     "haste_transpose_bf16": [P, P, I64, I64, P],
     "haste_ffi_rewire": [P, P, P, I64, I64, I64, I64, I64, I32, F32, I32, I32, I32, I32, U64, U32, P, P],
     "haste_ffi_rewire_ex": [P, P, P, I64, I64, I64, I64, I64, I32, I32, F32, I64, I32, I32, I32, U64, U32, P, P, P],
+    "haste_ffi_rewire_select_begin": [P, I64, I64, I64, I32, P, P],
+    "haste_ffi_rewire_select_refine": [I64, I64, I64, I64, P, P],
+    "haste_ffi_rewire_select_finish": [I64, I64, I64, P, P],
+    "haste_ffi_rewire_prepared": [P, P, P, I64, I64, I64, I64, I64, I32, U32, I32, I32, I32, U64, U32, P, P, P],
     "haste_ffi_step": [P, P, I64, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64, U32, U32, P],
     "haste_topk_update": [P, I64, I64, I64, I64, I32, P, P, P],
     "haste_ffi_check_locations": [P, I64, I64, P],

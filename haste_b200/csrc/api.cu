@@ -297,6 +297,42 @@ int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t 
                        step, scratch, changed, static_cast<cudaStream_t>(stream));
 }
 
+int haste_ffi_rewire_select_begin(const void* w, int64_t F, int64_t L, int64_t G, int32_t score_mode, void* scratch, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire_select_begin";
+  REQUIRE_PTR(w, who); REQUIRE_PTR(scratch, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(scratch, who);
+  if (int rc = validate_shape(who, 1, 1, F, L, G)) return rc;
+  if (score_mode < 0 || score_mode > 1) return fail(HASTE_ERR_BAD_ARG, "%s: bad score_mode", who);
+  return launch_rewire_select_begin(w, F, L, G, score_mode, scratch, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_rewire_select_refine(int64_t F, int64_t L, int64_t G, int64_t k_layer, void* scratch, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire_select_refine";
+  REQUIRE_PTR(scratch, who);
+  if (int rc = validate_shape(who, 1, 1, F, L, G)) return rc;
+  if (k_layer < 1 || k_layer >= (1ll << 32)) return fail(HASTE_ERR_BAD_ARG, "%s: k_layer=%lld outside [1, 2^32)", who, (long long)k_layer);
+  return launch_rewire_select_refine(F, L, G, k_layer, scratch, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_rewire_select_finish(int64_t F, int64_t L, int64_t G, void* scratch, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire_select_finish";
+  REQUIRE_PTR(scratch, who);
+  if (int rc = validate_shape(who, 1, 1, F, L, G)) return rc;
+  return launch_rewire_select_finish(F, L, G, scratch, static_cast<cudaStream_t>(stream));
+}
+
+int haste_ffi_rewire_prepared(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0,
+                              int32_t score_mode, uint32_t tie_base, int32_t regrow_mode, int32_t init_mode, int32_t regroup, uint64_t seed,
+                              uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream) {
+  const char* who = "haste_ffi_rewire_prepared";
+  REQUIRE_PTR(w, who); REQUIRE_PTR(loc, who); REQUIRE_PTR(scratch, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(scratch, who);
+  if (int rc = validate_shape(who, 1, D, F, L, G)) return rc;
+  if (score_mode < 0 || score_mode > 1 || regrow_mode < 0 || regrow_mode > 1 || init_mode < 0 || init_mode > 1)
+    return fail(HASTE_ERR_BAD_ARG, "%s: bad mode", who);
+  if (regrow_mode == 1 && D < 2 * F) return fail(HASTE_ERR_UNSUPPORTED, "%s: 'unused' regrow needs D >= 2*F", who);
+  return launch_rewire(w, loc, mom_w, D, F, L, G, group0, score_mode, 3, 0.f, 0, regrow_mode, init_mode, regroup, seed, step, scratch, changed,
+                       static_cast<cudaStream_t>(stream), tie_base);
+}
+
 int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int32_t k, float* vals, int32_t* idx,
                       haste_stream_t stream) {
   const char* who = "haste_topk_update";

@@ -5,7 +5,7 @@
 // highest-numbered CTAs).  Per group and per 128-row batch tile three UMMA products run out of the same three
 // shared-memory tiles (none is ever transposed or re-gathered; the 128-byte-swizzled "row block" layout serves both
 // operand majors):
-//     X tile [F + 16 rows = slots][128 batch]  rows of xt gathered with cp.async (16 B each); row F holds ones
+//     X tile [F + 16 rows = slots][128 batch]  rows of xt gathered by TMA (tile::gather4); row F holds ones
 //     W tile [G rows = labels][F]               the group's weights, loaded by TMA through a 2-D tensor map
 //     B tile [G rows][16]                       (no swizzle) the group's bias in column 0, zeros elsewhere
 //     Y tile [128 batch][G]                     dLoss/dlogit for the tile, written by the loss-epilogue warps
@@ -15,8 +15,8 @@
 //   backward-weights   dW [l,k] (TMEM, F+16 cols, accumulated over the batch tiles; M = G)
 //                                                = Y^T (MN-major A) * X (K-major B),         K = 128; column F of the
 //                                                  result (the ones row) is the bias gradient
-// Warp roles: warp 0 producer (W tile by TMA; X rows by cp.async whose completion arrives on the stage's barrier by
-// itself, so the warp never waits for a copy and keeps several tiles in flight),
+// Warp roles: 4 producer warps (warp 0 loads the W tile through a tensor map; all four gather X tiles with TMA
+// tile::gather4, one instruction per lane and tile — the gather rate grows with the number of issuing warps),
 // warp 1 issues forward + backward-features, warp 3 issues backward-weights, 8 loss-epilogue warps turn Z into dY
 // (bf16 rounding of the logit, loss gradient, target bits) and store it swizzled, 4 (F=64) or 8 (F=128) scatter
 // warps drain dXg (TMEM -> registers -> coalesced red.global.add into dxt rows), 8 update warps apply SGD + weight
@@ -62,7 +62,8 @@ struct Cfg {
   static constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
   static constexpr int OFF_BT = OFF_Y + NYS * YSTAGE;
   static constexpr int OFF_LOC = OFF_BT + 2 * BTILE;           // u32 [2][F]: element offset loc * B of each slot's dxt row
-  static constexpr int OFF_YB = OFF_LOC + 2 * F * 4;           // u32 [2][BT][G/32]: target bits
+  static constexpr int OFF_LOCR = OFF_LOC + 2 * F * 4;         // int [4][F]: each producer warp's copy of the group's (clamped) indices, for the gather
+  static constexpr int OFF_YB = OFF_LOCR + 4 * F * 4;          // u32 [2][BT][G/32]: target bits
   static constexpr int OFF_BAR = OFF_YB + 2 * BT * (G / 32) * 4;
   static constexpr int OFF_MISC = OFF_BAR + 32 * 8;            // tmem base address, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;      // + slack for the 1024-byte alignment of the base
@@ -81,11 +82,11 @@ struct Cfg {
   static_assert(TM_DW + FR <= TM_COLS, "TMEM budget");
 
   static constexpr int N_EA = 8;                      // loss-epilogue warps: 4 TMEM lane quarters x 2 column halves
-  static constexpr int EBS = 64;                      // slots per scatter warp
-  static constexpr int N_EB = 4 * (F / EBS);          // scatter warps: 4 TMEM lane quarters x 64-slot chunks
+  static constexpr int EBS = F;                       // slots per scatter warp
+  static constexpr int N_EB = 4 * (F / EBS);          // scatter warps: one per TMEM lane quarter
   static constexpr int N_UP = 8;                      // update warps: 4 TMEM lane quarters x 2 slot halves
   static constexpr int W_EA = 4, W_EB = W_EA + N_EA, W_UP = W_EB + N_EB;
-  static constexpr int NPW = (F == 64) ? 4 : 2;       // producer warps: warp 0, warp 2, then extra warps after the update warps
+  static constexpr int NPW = 4;                       // producer warps: warp 0, warp 2, then extra warps after the update warps
   static_assert(NPW >= 1 && NPW <= NXS, "a producer must not run more than one phase ahead on any stage barrier");
   static constexpr int W_XP = W_UP + N_UP;            // first extra producer warp
   static constexpr int NTHREADS = (W_XP + (NPW > 2 ? NPW - 2 : 0)) * 32;
@@ -140,7 +141,7 @@ __device__ __forceinline__ float tanh_approx(float x) {
 
 template <int G_, int F_, int LOSS, bool WITH_LOSS, bool MOM, bool DEBUG>
 __global__ void __launch_bounds__(Cfg<G_, F_>::NTHREADS, 1)
-ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CUtensorMap tm_w) {
+ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w) {
   using C = Cfg<G_, F_>;
   constexpr int G = C::G, F = C::F, BT = C::BT, FR = C::FR, NXS = C::NXS, NYS = C::NYS, NDX = C::NDX;
   constexpr int XBLK = C::XBLK, XSTAGE = C::XSTAGE, WBLK = C::WBLK, WSTAGE = C::WSTAGE, YBLK = C::YBLK, YSTAGE = C::YSTAGE;
@@ -167,7 +168,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 
   // ---------------- one-time setup
   if (tid == 0) {
-    for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 32); mbar_init(bar(C::B_XEMPTY + i), 1); }   // X stage: one asynchronous arrival per producer lane
+    for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 1); mbar_init(bar(C::B_XEMPTY + i), 1); }   // X stage: one arrival that announces the gathered bytes
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::B_WFULL + i), 1);  mbar_init(bar(C::B_WEMPTY + i), 1);
       mbar_init(bar(C::B_ZFULL + i), 1);  mbar_init(bar(C::B_ZEMPTY + i), N_EA);
@@ -213,9 +214,8 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
     // ================================================================ producers
     // Per group: the index row (as dxt row offsets for the scatter warps) and the bias column go to shared memory
     // with ordinary stores, the W tile comes through the tensor map.  Per batch tile: F index rows of xt, 256 bytes
-    // each, as 16-byte cp.async copies (two rows per warp instruction) written at their swizzled positions; each
-    // lane then posts an asynchronous arrival that fires when its copies have landed.  (TMA tile::gather4 was
-    // measured for this gather: about 26 cycles per 128-byte row and SM, three times the tile budget.)
+    // each, as F/4 TMA gather4 loads per 64-batch block (four index rows per instruction, landing at their swizzled
+    // positions); lane 0 arms the stage's barrier with the byte count, then every lane issues its share.
     // The W item of every group belongs to producer 0; the X items (one per batch tile) are dealt round-robin.
     int it = 0;                  // X items so far (all producers count all of them)
     int w_armed = 0;             // W stages armed so far
@@ -261,6 +261,13 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
       }
       __syncwarp();
       }
+      // this warp's own copy of the index row, read back four slots at a time for the gathers
+      int* locr = reinterpret_cast<int*>(sm + C::OFF_LOCR) + prod_id * F;
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < F / 32; ++j) locr[lane + 32 * j] = locv[j];
+      __syncwarp();
+      const int4* lr4 = reinterpret_cast<const int4*>(locr);
       for (int t = 0; t < T; ++t, ++it) {
         if (it % C::NPW != prod_id) continue;
         const int xs = it % NXS;
@@ -269,20 +276,14 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
         if (!okx || *abort_flag) continue;
         const int b0 = tile_b0(t);
         const uint32_t xb = sbase + C::OFF_X + xs * XSTAGE;
-        const int j = lane & 15;                     // 16-byte chunk along the batch: 8 rows each
-        const bool valid = b0 + j * 8 < a.B;
-        const uint32_t dcol = (j >> 3) * XBLK + ((j & 7) << 4);
-        const __nv_bfloat16* src0 = a.xt + b0 + j * 8;
+        if (lane == 0) mbar_arrive_expect_tx(bar(C::B_XFULL + xs), F * 256);
+        __syncwarp();
 #pragma unroll
-        for (int jj = 0; jj < F / 32; ++jj) {        // index values jj*32 .. jj*32+31 live in locv[jj] of lane (slot & 31)
-#pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int k = jj * 32 + i * 2 + (lane >> 4);         // slot: two per iteration, 16 lanes each
-            const int lk = __shfl_sync(0xffffffffu, locv[jj], k & 31);
-            cp_async16(xb + ((dcol + k * 128) ^ ((k & 7) << 4)), valid ? src0 + static_cast<int64_t>(lk) * a.B : a.xt, valid);
-          }
+        for (int i = lane; i < 2 * (F / 4); i += 32) {        // one gather4 per four slots and 64-batch block
+          const int blk = i / (F / 4), r4 = i % (F / 4);
+          const int4 lr = lr4[r4];
+          tma_gather4(xb + blk * XBLK + r4 * 512, &tm_x, b0 + blk * 64, lr.x, lr.y, lr.z, lr.w, bar(C::B_XFULL + xs));
         }
-        cp_async_mbar_arrive_noinc(bar(C::B_XFULL + xs));   // each lane's arrival fires when its copies have landed
         my_last = it;
       }
     }
@@ -804,8 +805,9 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
   a.stall_tile = dump ? take_stall_tile() : -1;
   a.z_dump = dump ? static_cast<__nv_bfloat16*>(dump->z) : nullptr; a.ldz = dump ? dump->ldz : 0;
   a.dw_dump = dump ? static_cast<__nv_bfloat16*>(dump->dw) : nullptr; a.db_dump = dump ? static_cast<__nv_bfloat16*>(dump->dbias) : nullptr;
-  CUtensorMap tm_w;
-  // W [L][F]: one box = 64 slots x G labels
+  CUtensorMap tm_x, tm_w;
+  // xt [D][B]: one box = 64 batch columns of one row (gather4 stacks four rows); W [L][F]: one box = 64 slots x G labels
+  if (int rc = make_tmap_bf16_2d(&tm_x, xt, static_cast<uint64_t>(B), static_cast<uint64_t>(D), static_cast<uint64_t>(B) * 2, 64, 1)) return rc;
   if (int rc = make_tmap_bf16_2d(&tm_w, u.w, static_cast<uint64_t>(F_), static_cast<uint64_t>(L), static_cast<uint64_t>(F_) * 2, 64, G_)) return rc;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -819,7 +821,7 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
     auto k = ffi_train_step_sm100_kernel<G_, F_, LK, WLOSS, MOMF, DBG>;                                             \
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);            \
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));         \
-    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_w);                                                        \
+    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_x, tm_w);                                                  \
   }
 #define HASTE_S100_BY_LOSS(WLOSS, MOMF, DBG)                                                                       \
   { if (loss_kind == HASTE_LOSS_BCE) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, WLOSS, MOMF, DBG) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, WLOSS, MOMF, DBG) }

@@ -71,6 +71,10 @@ int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st);
 // layer-wide count and scratch holds HASTE_REWIRE_SCRATCH_WORDS(NG, F) words)
 int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int score_mode, int prune_mode,
                   float threshold, int64_t n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,
-                  void* scratch, int32_t* changed, cudaStream_t st);
+                  void* scratch, int32_t* changed, cudaStream_t st, uint32_t tie_base = 0);
+// layer-wide selection in phases, for a layer sharded over ranks (the caller sums the histograms between the phases)
+int launch_rewire_select_begin(const void* w, int64_t F, int64_t L, int64_t G, int score_mode, void* scratch, cudaStream_t st);
+int launch_rewire_select_refine(int64_t F, int64_t L, int64_t G, int64_t k, void* scratch, cudaStream_t st);
+int launch_rewire_select_finish(int64_t F, int64_t L, int64_t G, void* scratch, cudaStream_t st);
 
 }  // namespace haste

@@ -4,7 +4,7 @@
 //   haste_probe_red_rate     fp32 reduce-add into a small [D,B] array (the dX scatter): scalar coalesced red, red.v4
 //                            along one row, red.v4 across 32 rows (what a transposed accumulator would issue)
 //   haste_probe_gather_rate  gathering 64 rows x 256 B of xt per tile into swizzled shared memory: TMA tile::gather4
-//                            against cp.async from 1, 2 or 4 warps with asynchronous barrier arrival
+//                            issued by 1, 2 or 4 warps against cp.async from 1, 2 or 4 warps with asynchronous barrier arrival
 //   haste_probe_umma_rate    back-to-back tcgen05.mma (M = 128, K = 16) at the step's N and operand majors
 #include "common.cuh"
 #include "runtime.h"
@@ -68,11 +68,12 @@ __global__ void __launch_bounds__(192) gather_kernel(const __nv_bfloat16* xt, co
   __shared__ int rows_s[G_STAGES][G_ROWS];
   volatile int* abort_flag = &abort_word;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_prod = mode == 0 ? 1 : mode;            // mode 0: TMA gather4 from one warp; mode 1/2/4: cp.async from that many warps
+  const bool tma = mode == 0 || mode >= 10;           // mode 0 / 12 / 14: TMA gather4 issued by 1 / 2 / 4 warps; mode 1 / 2 / 4: cp.async from that many warps
+  const int n_prod = mode == 0 ? 1 : (mode >= 10 ? mode - 10 : mode);
   auto full = [&](int s) { return smem_u32(&bars[s]); };
   auto empty = [&](int s) { return smem_u32(&bars[G_STAGES + s]); };
   if (tid == 0) {
-    for (int s = 0; s < G_STAGES; ++s) { mbar_init(full(s), mode == 0 ? 1 : 32); mbar_init(empty(s), 1); }
+    for (int s = 0; s < G_STAGES; ++s) { mbar_init(full(s), tma ? 1 : 32); mbar_init(empty(s), 1); }
     mbar_fence_init();
     abort_word = 0;
   }
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(192) gather_kernel(const __nv_bfloat16* xt, co
       const uint32_t xb = sbase + st * G_STAGE;
       // 64 distinct rows: r_lo + a permutation step, so that neighbouring slots are not neighbouring rows
       const int my_row0 = r_lo + ((lane * 37) & 63), my_row1 = r_lo + (((lane + 32) * 37) & 63);
-      if (mode == 0) {
+      if (tma) {
         rows_s[st][lane] = my_row0; rows_s[st][lane + 32] = my_row1;
         __syncwarp();
         if (lane == 0) mbar_arrive_expect_tx(full(st), G_ROWS * 256);
@@ -182,8 +183,10 @@ int haste_probe_red_rate(float* dxt, int64_t D, int64_t B, int32_t mode, int32_t
 }
 
 int haste_probe_gather_rate(const void* xt, int64_t D, int64_t B, int32_t mode, int32_t tiles_per_cta, haste_stream_t stream) {
-  if (xt == nullptr || D < 128 || B < 128 || (B % 128) != 0 || !(mode == 0 || mode == 1 || mode == 2 || mode == 4) || tiles_per_cta < 1)
-    return fail(HASTE_ERR_BAD_ARG, "haste_probe_gather_rate: bad arguments (D >= 128, B a multiple of 128, mode 0 = TMA gather4, 1/2/4 = cp.async warps)");
+  if (xt == nullptr || D < 128 || B < 128 || (B % 128) != 0 || !(mode == 0 || mode == 1 || mode == 2 || mode == 4 || mode == 12 || mode == 14) ||
+      tiles_per_cta < 1)
+    return fail(HASTE_ERR_BAD_ARG, "haste_probe_gather_rate: bad arguments (D >= 128, B a multiple of 128, mode 0/12/14 = TMA gather4 from 1/2/4 warps, "
+                "1/2/4 = cp.async warps)");
   if (int rc = report_pending_status("haste_probe_gather_rate")) return rc;
   int* err = nullptr;
   if (int rc = device_status_word(&err)) return rc;

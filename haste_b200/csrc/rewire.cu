@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(256) select_equal_count_kernel(const float* __
     if (bits[i] == T) atomicAdd(&sel[2 + i / F], 1u);
 }
 // exclusive prefix over the groups of the per-group equal counts, in place
-__global__ void __launch_bounds__(SEL_THREADS) select_scan_kernel(uint32_t* __restrict__ eq, int NG) {
+// *total receives the number of scores equal to T in this shard
+__global__ void __launch_bounds__(SEL_THREADS) select_scan_kernel(uint32_t* __restrict__ eq, int NG, uint32_t* __restrict__ total) {
   __shared__ int part[SEL_THREADS];
   const int tid = threadIdx.x;
   const int chunk = (NG + SEL_THREADS - 1) / SEL_THREADS, lo = min(NG, tid * chunk), hi = min(NG, lo + chunk);
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_scan_kernel(uint32_t* __re
   if (tid == 0) {
     int run = 0;
     for (int i = 0; i < SEL_THREADS; ++i) { const int v = part[i]; part[i] = run; run += v; }
+    *total = static_cast<uint32_t>(run);
   }
   __syncthreads();
   int run = part[tid];
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_scan_kernel(uint32_t* __re
 __global__ void __launch_bounds__(RW_THREADS) ffi_rewire_kernel(uint16_t* __restrict__ w, int32_t* __restrict__ loc, float* __restrict__ mom,
                                                                 int D, int F, int64_t L, int G, int64_t group0, int score_mode, int prune_mode,
                                                                 float threshold, int n_prune, const uint32_t* __restrict__ sel,
-                                                                int regrow_mode, int init_mode,
+                                                                uint32_t tie_base, int regrow_mode, int init_mode,
                                                                 int regroup, float bound, uint64_t seed, uint32_t step,
                                                                 int32_t* __restrict__ changed) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -191,9 +193,10 @@ __global__ void __launch_bounds__(RW_THREADS) ffi_rewire_kernel(uint16_t* __rest
       if (sb != T) {
         p = sb < T;
       } else {
-        int rank = static_cast<int>(sel[2 + g]);
+        // rank among the scores equal to T in flat (group, slot) order; tie_base counts those on lower-ranked shards
+        int64_t rank = static_cast<int64_t>(tie_base) + sel[2 + g];
         for (int j = 0; j < tid; ++j) rank += __float_as_uint(score[j]) == T;
-        p = rank < static_cast<int>(sel[1]);
+        p = rank < static_cast<int64_t>(sel[1]);
       }
     } else {
       int rank = 0;
@@ -275,9 +278,65 @@ __global__ void __launch_bounds__(RW_THREADS) ffi_rewire_kernel(uint16_t* __rest
   if (tid == 0 && changed != nullptr && n_pruned) atomicAdd(changed, n_pruned);
 }
 
+// Scratch of the layer-wide selection (32-bit words): scores[NG*F] | sel[2 + NG] | hist_hi[65536] | hist_lo[65536] |
+// tmp[8] = {k, hi digit, k inside that bin, lo digit, scores equal to T in this shard, -, -, -}
+struct SelectScratch {
+  float* scores;
+  uint32_t *sel, *hist_hi, *hist_lo, *tmp;
+  int64_t n;
+};
+static SelectScratch select_scratch(void* scratch, int64_t NG, int64_t F) {
+  SelectScratch s;
+  s.scores = static_cast<float*>(scratch);
+  s.sel = reinterpret_cast<uint32_t*>(s.scores + NG * F);
+  s.hist_hi = s.sel + 2 + NG;
+  s.hist_lo = s.hist_hi + 65536;
+  s.tmp = s.hist_lo + 65536;
+  s.n = NG * F;
+  return s;
+}
+
+// Phase 1: scores of this shard and the histogram of their upper 16 bits.
+int launch_rewire_select_begin(const void* w, int64_t F, int64_t L, int64_t G, int score_mode, void* scratch, cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  SelectScratch s = select_scratch(scratch, NG, F);
+  cudaError_t e = cudaMemsetAsync(s.sel, 0, sizeof(uint32_t) * static_cast<size_t>(2 + NG + 2 * 65536 + 8), st);
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  e = cudaFuncSetAttribute(ffi_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(size_t(G) * F * 2));
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  ffi_scores_kernel<<<static_cast<unsigned>(NG), RW_THREADS, size_t(G) * F * 2, st>>>((const uint16_t*)w, int(F), L, int(G), score_mode, s.scores, s.hist_hi);
+  return check_launch("ffi_scores_kernel");
+}
+// Phase 2: hist_hi now holds the histogram of the WHOLE layer (summed over the shards by the caller, or this shard's
+// when there is one); find the digit of the k-th smallest score and histogram the lower 16 bits inside it.
+int launch_rewire_select_refine(int64_t F, int64_t L, int64_t G, int64_t k, void* scratch, cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  SelectScratch s = select_scratch(scratch, NG, F);
+  const uint32_t k32 = static_cast<uint32_t>(k);
+  cudaError_t e = cudaMemcpyAsync(s.tmp, &k32, sizeof(uint32_t), cudaMemcpyHostToDevice, st);     // pageable source: copied before the call returns
+  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMemcpyAsync: %s", cudaGetErrorString(e));
+  select_pick16_kernel<<<1, SEL_THREADS, 0, st>>>(s.hist_hi, s.tmp, s.tmp + 1, s.tmp + 2);
+  select_hist_lo_kernel<<<static_cast<unsigned>(grid_for(s.n, 256)), 256, 0, st>>>(s.scores, s.n, s.tmp + 1, s.hist_lo);
+  return check_launch("select_hist_lo_kernel");
+}
+// Phase 3: hist_lo holds the whole layer's histogram inside the digit; fix the threshold T = k-th smallest score, the
+// number of scores equal to T that are pruned (sel[1], layer-wide), this shard's per-group positions among the scores
+// equal to T (sel[2..]) and their count (tmp[4]).
+int launch_rewire_select_finish(int64_t F, int64_t L, int64_t G, void* scratch, cudaStream_t st) {
+  const int64_t NG = (L + G - 1) / G;
+  SelectScratch s = select_scratch(scratch, NG, F);
+  select_pick16_kernel<<<1, SEL_THREADS, 0, st>>>(s.hist_lo, s.tmp + 2, s.tmp + 3, s.sel + 1);
+  select_equal_count_kernel<<<static_cast<unsigned>(grid_for(s.n, 256)), 256, 0, st>>>(s.scores, s.n, int(F), s.tmp + 1, s.tmp + 3, s.sel);
+  select_scan_kernel<<<1, SEL_THREADS, 0, st>>>(s.sel + 2, int(NG), s.tmp + 4);
+  return check_launch("select_scan_kernel");
+}
+
+// prune_mode 2: layer-wide fraction selected inside this call (one shard = the whole layer);
+// prune_mode 3: the selection was prepared in `scratch` by the three phases above (layer sharded over ranks) and
+//               tie_base scores equal to the threshold belong to lower-ranked shards.
 int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0, int score_mode, int prune_mode,
                   float threshold, int64_t n_prune, int regrow_mode, int init_mode, int regroup, uint64_t seed, uint32_t step,
-                  void* scratch, int32_t* changed, cudaStream_t st) {
+                  void* scratch, int32_t* changed, cudaStream_t st, uint32_t tie_base) {
   const int64_t NG = (L + G - 1) / G;
   const size_t sm = size_t(G) * F * 2 + size_t(F) * 4 * 4;
   cudaError_t e = cudaFuncSetAttribute(ffi_rewire_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
@@ -285,33 +344,16 @@ int launch_rewire(void* w, int32_t* loc, float* mom, int64_t D, int64_t F, int64
   if (changed != nullptr) cudaMemsetAsync(changed, 0, sizeof(int32_t), st);
   const uint32_t* sel = nullptr;
   if (prune_mode == 2) {
-    // scratch (32-bit words): scores[NG*F] | sel[2 + NG] | hist_hi[65536] | hist_lo[65536] | tmp[4] = {k, hi, k_in_bin, lo}
-    float* scores = static_cast<float*>(scratch);
-    uint32_t* selw = reinterpret_cast<uint32_t*>(scores + NG * F);
-    uint32_t* hist_hi = selw + 2 + NG;
-    uint32_t* hist_lo = hist_hi + 65536;
-    uint32_t* tmp = hist_lo + 65536;
-    const int64_t n = NG * F;
-    e = cudaMemsetAsync(selw, 0, sizeof(uint32_t) * static_cast<size_t>(2 + NG + 2 * 65536 + 4), st);
-    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
-    const uint32_t k32 = static_cast<uint32_t>(n_prune);
-    e = cudaMemcpyAsync(tmp, &k32, sizeof(uint32_t), cudaMemcpyHostToDevice, st);     // pageable source: copied before the call returns
-    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaMemcpyAsync: %s", cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(ffi_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(size_t(G) * F * 2));
-    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    ffi_scores_kernel<<<static_cast<unsigned>(NG), RW_THREADS, size_t(G) * F * 2, st>>>((const uint16_t*)w, int(F), L, int(G), score_mode, scores, hist_hi);
-    select_pick16_kernel<<<1, SEL_THREADS, 0, st>>>(hist_hi, tmp, tmp + 1, tmp + 2);
-    const unsigned sel_grid = static_cast<unsigned>(grid_for(n, 256));
-    select_hist_lo_kernel<<<sel_grid, 256, 0, st>>>(scores, n, tmp + 1, hist_lo);
-    select_pick16_kernel<<<1, SEL_THREADS, 0, st>>>(hist_lo, tmp + 2, tmp + 3, selw + 1);
-    select_equal_count_kernel<<<sel_grid, 256, 0, st>>>(scores, n, int(F), tmp + 1, tmp + 3, selw);
-    select_scan_kernel<<<1, SEL_THREADS, 0, st>>>(selw + 2, int(NG));
-    sel = selw;
+    if (int rc = launch_rewire_select_begin(w, F, L, G, score_mode, scratch, st)) return rc;
+    if (int rc = launch_rewire_select_refine(F, L, G, n_prune, scratch, st)) return rc;
+    if (int rc = launch_rewire_select_finish(F, L, G, scratch, st)) return rc;
+    tie_base = 0;
   }
+  if (prune_mode == 2 || prune_mode == 3) sel = select_scratch(scratch, NG, F).sel;
   const float bound = static_cast<float>(1.0 / sqrt(static_cast<double>(F)));
   ffi_rewire_kernel<<<static_cast<unsigned>(NG), RW_THREADS, sm, st>>>((uint16_t*)w, loc, mom, int(D), int(F), L, int(G), group0, score_mode,
-                                                                        prune_mode, threshold, static_cast<int>(n_prune), sel, regrow_mode,
-                                                                        init_mode, regroup, bound, seed, step, changed);
+                                                                        prune_mode == 3 ? 2 : prune_mode, threshold, static_cast<int>(n_prune), sel,
+                                                                        tie_base, regrow_mode, init_mode, regroup, bound, seed, step, changed);
   return check_launch("ffi_rewire_kernel");
 }
 

@@ -1,4 +1,5 @@
-// sm_100a primitives in inline PTX: mbarrier with bounded waits, tiled TMA loads (never multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
+// sm_100a primitives in inline PTX: mbarrier with bounded waits, TMA loads (tiled and tile::gather4, never
+// multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
 // zero fill, bulk reduce-add to global.
 #pragma once
 #include <cuda_runtime.h>
@@ -91,6 +92,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
   asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
                "l"(tmap), "r"(x), "r"(y), "r"(bar)
                : "memory");
+}
+
+// Four rows r0..r3 of a 2-D tensor (box = {columns, 1 row}) starting at column x, stacked as four consecutive rows
+// at dst; with a 128-byte box and the 128-byte swizzle each row lands exactly as the UMMA row-block layout wants it.
+// One issuing warp sustains about one 16 KB tile per 2,600 cycles on a B200, four warps one per 950 (the same as
+// cp.async from as many warps): the rate is set by the loads in flight per issuer, so the gather is spread over warps.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int x, int r0, int r1, int r2, int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+      : "memory");
 }
 
 // ---------------------------------------------------------------- cp.async (16 B, zero fill when !valid)

@@ -242,7 +242,43 @@ def rewire(w, loc, mom_w, D, G, group0, prune_mode, threshold, n_prune, regrow_m
 
 def rewire_scratch_words(NG, F):
     """32-bit words of device scratch for layer-wide fraction pruning (HASTE_REWIRE_SCRATCH_WORDS)."""
-    return NG * F + NG + 2 + 2 * 65536 + 4
+    return NG * F + NG + 2 + 2 * 65536 + 8
+
+
+class LayerwideSelect:
+    """The layer-wide fraction selection of one label shard, in phases (haste_ffi_rewire_select_*): between the phases
+    the caller sums ``hist_hi`` / ``hist_lo`` over the shards and gathers ``ties``; ``apply`` then rewires the shard."""
+
+    def __init__(self, w, G, score_mode):
+        _req(w, "weights", torch.bfloat16)
+        self.w, self.G, self.score_mode = w, int(G), int(score_mode)
+        self.L, self.F = w.shape
+        self.NG = (self.L + self.G - 1) // self.G
+        self.scratch = torch.empty(rewire_scratch_words(self.NG, self.F), dtype=torch.int32, device=w.device)
+        hi = self.NG * self.F + 2 + self.NG
+        self.hist_hi = self.scratch[hi:hi + 65536]                 # views into the scratch: summed in place by the caller
+        self.hist_lo = self.scratch[hi + 65536:hi + 2 * 65536]
+        self.ties = self.scratch[hi + 2 * 65536 + 4:hi + 2 * 65536 + 5]
+
+    def begin(self):
+        with torch.cuda.device(self.w.device):
+            check(lib.haste_ffi_rewire_select_begin(_ptr(self.w), self.F, self.L, self.G, self.score_mode, _ptr(self.scratch), _stream(self.w)),
+                  "rewire_select_begin")
+
+    def refine(self, k_layer):
+        with torch.cuda.device(self.w.device):
+            check(lib.haste_ffi_rewire_select_refine(self.F, self.L, self.G, int(k_layer), _ptr(self.scratch), _stream(self.w)), "rewire_select_refine")
+
+    def finish(self):
+        with torch.cuda.device(self.w.device):
+            check(lib.haste_ffi_rewire_select_finish(self.F, self.L, self.G, _ptr(self.scratch), _stream(self.w)), "rewire_select_finish")
+
+    def apply(self, loc, mom_w, D, group0, tie_base, regrow_mode, init_mode, regroup, seed, step, changed=None):
+        _req(loc, "group_locations", torch.int32)
+        with torch.cuda.device(self.w.device):
+            check(lib.haste_ffi_rewire_prepared(_ptr(self.w), _ptr(loc), _ptr(mom_w), D, self.F, self.L, self.G, group0, self.score_mode,
+                                                int(tie_base), regrow_mode, init_mode, int(bool(regroup)), seed, step, _ptr(self.scratch),
+                                                _ptr(changed), _stream(self.w)), "rewire_prepared")
 
 
 def rewire_ex(w, loc, mom_w, D, G, group0, score_mode, prune_mode, threshold, n_prune, regrow_mode, init_mode, regroup, seed, step,

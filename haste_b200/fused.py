@@ -291,6 +291,48 @@ class ShardedFFILayer:
         return dxt
 
 
+def layerwide_prune_count(total_groups, fan_in, fraction):
+    """Number of (group, slot) pairs the layer-wide fraction rule prunes: int(NG * F * fraction) over the WHOLE layer
+    (src/group_fanin_real.py:232-250), whatever the sharding."""
+    return int(int(total_groups) * int(fan_in) * float(fraction))
+
+
+def tie_base_for_rank(ties_per_rank, rank):
+    """Scores equal to the selection threshold are pruned in flat (group, slot) order of the whole layer; ranks hold
+    contiguous label ranges in rank order, so a rank's ties come after those of all lower ranks."""
+    return int(sum(int(t) for t in ties_per_rank[:rank]))
+
+
+def rewire_layerwide_sharded(shard, fraction, total_groups, rank, world_size, process_group=None, *, score_mode="mean", regrow="replace",
+                             init_mode="zero", regroup=False, seed=0, step=0):
+    """Layer-wide fraction rewire of a label-sharded layer: every rank calls this with its ``FusedFFIShard``; the
+    prune set is the one a single device holding the whole layer would choose.  Two all-reduces of a 65,536-bin
+    histogram and one all-gather of a counter are the only exchanges.  Returns the number of pairs pruned on this rank."""
+    import torch.distributed as dist
+    k = layerwide_prune_count(total_groups, shard.F, fraction)
+    if k == 0:
+        return 0
+    sel = _ffi.LayerwideSelect(shard.w, shard.G, {"mean": 0, "max": 1}[score_mode])
+    multi = world_size > 1
+    sel.begin()
+    if multi:
+        dist.all_reduce(sel.hist_hi, op=dist.ReduceOp.SUM, group=process_group)
+    sel.refine(k)
+    if multi:
+        dist.all_reduce(sel.hist_lo, op=dist.ReduceOp.SUM, group=process_group)
+    sel.finish()
+    ties = [sel.ties.clone() for _ in range(world_size)]
+    if multi:
+        dist.all_gather(ties, sel.ties.clone(), group=process_group)
+    else:
+        ties = [sel.ties]
+    base = tie_base_for_rank([int(t.item()) for t in ties], rank)
+    changed = torch.zeros(1, dtype=torch.int32, device=shard.w.device)
+    sel.apply(shard.loc, shard.mom_w, shard.D, shard.label0 // shard.G, base, {"replace": 0, "unused": 1}[regrow],
+              {"zero": 0, "random": 1}[init_mode], regroup, seed, step, changed)
+    return int(changed.item())
+
+
 def _sm_count(device):
     return torch.cuda.get_device_properties(device).multi_processor_count
 

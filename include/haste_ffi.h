@@ -240,12 +240,36 @@ int haste_ffi_rewire(void* w, int32_t* loc, float* mom_w,
  *                lowest flat (group, slot) index (the reference leaves them to torch.topk).
  * scratch (prune_mode 2 only, 16-byte aligned device memory): HASTE_REWIRE_SCRATCH_WORDS(NG, F) * 4 bytes.
  * Everything else as haste_ffi_rewire.  With a sharded layer "the whole layer" is this shard. */
-#define HASTE_REWIRE_SCRATCH_WORDS(NG, F) ((int64_t)(NG) * (F) + (NG) + 2 + 2 * 65536 + 4)
+#define HASTE_REWIRE_SCRATCH_WORDS(NG, F) ((int64_t)(NG) * (F) + (NG) + 2 + 2 * 65536 + 8)
 int haste_ffi_rewire_ex(void* w, int32_t* loc, float* mom_w,
                         int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0,
                         int32_t score_mode, int32_t prune_mode, float threshold, int64_t n_prune,
                         int32_t regrow_mode, int32_t init_mode, int32_t regroup,
                         uint64_t seed, uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream);
+
+/* The layer-wide fraction rule for a layer that is sharded over ranks (each rank holds a contiguous label range): the
+ * k = int(NG_layer * F * fraction) lowest scores of ALL shards are pruned, as src/group_fanin_real.py:232-250 does on
+ * one device.  Every rank makes the same four calls on its shard, with two sums and one gather in between:
+ *   haste_ffi_rewire_select_begin   scores of the shard; histogram of their upper 16 bits at word
+ *                                   HASTE_REWIRE_HIST_HI_WORD(NG,F) of scratch (65536 uint32)  -> sum it over the ranks
+ *   haste_ffi_rewire_select_refine  k_layer = the layer-wide count; histogram of the lower 16 bits inside the k-th
+ *                                   score's bin at HASTE_REWIRE_HIST_LO_WORD(NG,F)             -> sum it over the ranks
+ *   haste_ffi_rewire_select_finish  threshold and tie bookkeeping; the number of this shard's scores equal to the
+ *                                   threshold at HASTE_REWIRE_TIES_WORD(NG,F)                  -> gather over the ranks
+ *   haste_ffi_rewire_prepared       prune / regrow / re-initialise / regroup as haste_ffi_rewire_ex does, with
+ *                                   tie_base = the sum of that count over the lower-ranked shards (ties at the
+ *                                   threshold go to the lowest flat (group, slot) index of the whole layer)
+ * NG, L, group0 describe the shard; scratch as for haste_ffi_rewire_ex. */
+#define HASTE_REWIRE_HIST_HI_WORD(NG, F) ((int64_t)(NG) * (F) + 2 + (NG))
+#define HASTE_REWIRE_HIST_LO_WORD(NG, F) (HASTE_REWIRE_HIST_HI_WORD(NG, F) + 65536)
+#define HASTE_REWIRE_TIES_WORD(NG, F) (HASTE_REWIRE_HIST_LO_WORD(NG, F) + 65536 + 4)
+int haste_ffi_rewire_select_begin(const void* w, int64_t F, int64_t L, int64_t G, int32_t score_mode, void* scratch,
+                                  haste_stream_t stream);
+int haste_ffi_rewire_select_refine(int64_t F, int64_t L, int64_t G, int64_t k_layer, void* scratch, haste_stream_t stream);
+int haste_ffi_rewire_select_finish(int64_t F, int64_t L, int64_t G, void* scratch, haste_stream_t stream);
+int haste_ffi_rewire_prepared(void* w, int32_t* loc, float* mom_w, int64_t D, int64_t F, int64_t L, int64_t G, int64_t group0,
+                              int32_t score_mode, uint32_t tie_base, int32_t regrow_mode, int32_t init_mode, int32_t regroup,
+                              uint64_t seed, uint32_t step, void* scratch, int32_t* changed, haste_stream_t stream);
 
 /* One training step from the batch as the data loader delivers it: haste_ffi_step_prepare followed by
  * haste_ffi_train_step in one call (two launches, one crossing of the language boundary).  x bf16 [B,D]; coo int32
@@ -272,7 +296,7 @@ int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t 
  *                            (B % 128 == 0): mode 0 scalar red, one 128-byte transaction per warp instruction (what the
  *                            step issues); 1 red.v4 along one row; 2 red.v4 across 32 rows per warp instruction
  *   haste_probe_gather_rate  gathering `tiles_per_cta` tiles of 64 rows x 256 B of xt [D,B] (bf16) per SM into
- *                            swizzled shared memory: mode 0 TMA tile::gather4; 1, 2, 4 = cp.async from that many warps
+ *                            swizzled shared memory: mode 0 / 12 / 14 TMA tile::gather4 issued by 1 / 2 / 4 warps; 1, 2, 4 = cp.async from that many warps
  *   haste_probe_umma_rate    8 * iters back-to-back tcgen05.mma (M=128, K=16, given N and operand majors) on one SM;
  *                            cycles_out (device, 2 x int64) receives the cycles to issue them and to complete them */
 int haste_probe_red_rate(float* dxt, int64_t D, int64_t B, int32_t mode, int32_t tiles_per_cta, haste_stream_t stream);

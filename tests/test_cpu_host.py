@@ -212,3 +212,54 @@ def test_srsgd_loads_reference_optimizer_state(built_lib):
     # momentum 0.9 * 2 + 1 = 2.8; p = 1 - 0.5 * 2.8
     assert torch.allclose(p.data, torch.full((4, 3), 1.0 - 0.5 * 2.8))
     assert opt.param_groups[0]["seed"] == 131 and opt.param_groups[0]["step_count"] == 1
+
+
+_LW_WORKER = r"""
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from oracle import ffi_oracle as fo
+from haste_b200.fused import layerwide_prune_count, tie_base_for_rank
+rank, world = int(sys.argv[2]), 2
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[3], rank=rank, world_size=world)
+D, L, F, G, frac = 96, 64 * 9 + 5, 32, 64, 0.2
+inp = fo.make_inputs(2, D, L, F, G, 1, 1.1, seed=3)
+NG = (L + G - 1) // G
+g0, g1 = (0, 4) if rank == 0 else (4, NG)
+scores = fo.rewire_scores(inp["W"], G, NG, "max")                 # whole layer (for the check) ...
+mine = scores[g0:g1].reshape(-1)                                   # ... and this rank's shard
+bits = mine.view(np.uint32)
+k = layerwide_prune_count(NG, F, frac)
+# the three phases of the device selection, restated with numpy, with the same exchanges between them
+hist_hi = torch.from_numpy(np.bincount(bits >> 16, minlength=65536).astype(np.int64)); dist.all_reduce(hist_hi)
+c = np.cumsum(hist_hi.numpy()); hi = int(np.searchsorted(c, k)); k_in = k - (int(c[hi - 1]) if hi else 0)
+inbin = bits[(bits >> 16) == hi]
+hist_lo = torch.from_numpy(np.bincount(inbin & 0xFFFF, minlength=65536).astype(np.int64)); dist.all_reduce(hist_lo)
+c = np.cumsum(hist_lo.numpy()); lo = int(np.searchsorted(c, k_in)); take = k_in - (int(c[lo - 1]) if lo else 0)
+T = (hi << 16) | lo
+ties = torch.tensor([int((bits == T).sum())]); allt = [torch.zeros_like(ties) for _ in range(world)]; dist.all_gather(allt, ties)
+base = tie_base_for_rank([int(t) for t in allt], rank)
+rank_among_ties = base + np.cumsum(bits == T) - 1
+mask = (bits < T) | ((bits == T) & (rank_among_ties < take))
+want = fo.prune_mask(scores, "fraction", frac, None, "global")[g0:g1].reshape(-1)
+assert np.array_equal(mask, want), "prune set differs from the single-device rule"
+tot = torch.tensor([int(mask.sum())]); dist.all_reduce(tot)
+assert int(tot) == k
+dist.destroy_process_group()
+print("ok")
+"""
+
+
+def test_two_rank_gloo_layerwide_selection(tmp_path):
+    """Host logic of the cross-rank layer-wide rewire selection (count, exchanges, tie order) on two gloo ranks: the
+    union of the ranks' prune sets is the single-device rule's prune set."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "lw_worker.py"
+    script.write_text(_LW_WORKER)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(r), str(port)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0 and "ok" in o, o

@@ -515,3 +515,52 @@ def test_topk_chunked_matches_full(hb, cfg):
     if kk == k:   # the last kept value may tie with one that was cut off
         uniq[:, -1] &= (z == want_v[:, -1:]).sum(1) == 1
     assert torch.equal(got_i[uniq], want_i[uniq])
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(D=300, L=64 * 11 + 9, F=48, G=64, score="max", frac=0.1, regrow="unused", init="random", regroup=True, cuts=[3, 8]),
+    dict(D=768, L=128 * 300 + 11, F=64, G=128, score="max", frac=0.15, regrow="unused", init="zero", regroup=True, cuts=[40, 41, 200]),
+    dict(D=768, L=128 * 300 + 11, F=64, G=128, score="mean", frac=0.3, regrow="replace", init="random", regroup=False, cuts=[150]),
+])
+def test_rewire_layerwide_across_shards_bit_exact(hb, cfg):
+    """The layer-wide fraction rule on a layer cut into label shards (haste_ffi_rewire_select_* + _prepared): the
+    shards' histograms are summed between the phases and the tie counts gathered, exactly as ranks would exchange
+    them; the result must equal the oracle's (and the single-shard kernel's) rewire of the whole layer, bit for bit —
+    including which of the scores that tie at the threshold are pruned (max scores of bf16 magnitudes tie often)."""
+    ffi, _ = hb
+    from haste_b200.fused import layerwide_prune_count, tie_base_for_rank
+    D, L, F, G = cfg["D"], cfg["L"], cfg["F"], cfg["G"]
+    inp = fo.make_inputs(4, D, L, F, G, 1, 1.1, seed=23)
+    NG = (L + G - 1) // G
+    gen = torch.Generator().manual_seed(5)
+    loc0 = torch.randint(0, D, (NG, F), generator=gen, dtype=torch.int32) if cfg["regrow"] == "replace" else inp["loc"]
+    seed, step = 77, 4
+    W1, loc1, _ = fo.rewire(inp["W"], loc0, G, D, "fraction", cfg["frac"], None, init_mode=cfg["init"], regrow=cfg["regrow"],
+                            regroup=cfg["regroup"], seed=seed, step=step, group0=0, score_mode=cfg["score"], prune_scope="global")
+    bounds = [0] + cfg["cuts"] + [NG]
+    shards = []
+    for g0, g1 in zip(bounds, bounds[1:]):
+        l0, l1 = g0 * G, min(L, g1 * G)
+        shards.append(dict(g0=g0, w=inp["W"][l0:l1].clone().cuda(), loc=loc0[g0:g1].clone().cuda()))
+    k = layerwide_prune_count(NG, F, cfg["frac"])
+    sels = [ffi.LayerwideSelect(s["w"], G, 0 if cfg["score"] == "mean" else 1) for s in shards]
+    for s in sels:
+        s.begin()
+    total = sum(s.hist_hi.clone() for s in sels)
+    for s in sels:
+        s.hist_hi.copy_(total)
+        s.refine(k)
+    total = sum(s.hist_lo.clone() for s in sels)
+    for s in sels:
+        s.hist_lo.copy_(total)
+        s.finish()
+    ties = [int(s.ties.item()) for s in sels]
+    n_changed = 0
+    for r, (s, sh) in enumerate(zip(sels, shards)):
+        changed = torch.zeros(1, dtype=torch.int32, device="cuda")
+        s.apply(sh["loc"], None, D, sh["g0"], tie_base_for_rank(ties, r), 0 if cfg["regrow"] == "replace" else 1,
+                0 if cfg["init"] == "zero" else 1, cfg["regroup"], seed, step, changed)
+        n_changed += int(changed)
+    assert n_changed == k
+    assert np.array_equal(torch.cat([sh["loc"] for sh in shards]).cpu().numpy(), loc1.numpy()), "index table"
+    assert np.array_equal(_bits(torch.cat([sh["w"] for sh in shards])), fo._bf16_to_bits(W1)), "weights"
