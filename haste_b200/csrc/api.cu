@@ -4,8 +4,6 @@
 #include "common.cuh"
 #include "launchers.h"
 
-#include <string.h>
-#include <stdlib.h>
 
 namespace haste {
 

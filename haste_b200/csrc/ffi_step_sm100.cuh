@@ -648,8 +648,14 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
     const int e = warp - C::W_UP;
     const int q = warp & 3;
     const int kh = e >> 2;
-    const int row = q * C::ROWS_PER_Q + lane;      // label row inside the group
-    const bool lane_active = lane < C::ROWS_PER_Q;
+    // G = 64: only lanes 0-15 of a TMEM lane quarter hold accumulator rows, so lane l and lane l+16 share label row
+    // l: lane l keeps the lower 8 slots of every 16-slot piece, lane l+16 gets the upper 8 by shuffle — the whole
+    // warp works and a lane's 8 slots are exactly one Philox call, one 16-byte chunk of W and one 16-byte store.
+    constexpr bool SPLIT = C::ROWS_PER_Q == 16;
+    constexpr int NSL = SPLIT ? 8 : 16;            // slots per lane and piece
+    const int lrow = SPLIT ? (lane & 15) : lane;
+    const int half = SPLIT ? (lane >> 4) : 0;
+    const int row = q * C::ROWS_PER_Q + lrow;      // label row inside the group
     constexpr int NPC = UPS / 16;                  // pieces of 16 slots
     for (int gu = 0; gu < n_my_groups; ++gu) {
       const int gg = group_of(gu);
@@ -660,7 +666,7 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
       mbar_wait(bar(C::B_DWFULL), gu & 1, abort_flag, a.err, 15, WL);
       tc_fence_after();
       const uint32_t tdw = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DW;
-      uint32_t gw[UPS / 2];                       // this thread's gradients, bf16 pairs
+      uint32_t gw[UPS / 2];                       // this TMEM lane's gradients, bf16 pairs (garbage in lanes 16-31 when SPLIT)
       float gb = 0.f;
       {
         __syncwarp();
@@ -682,59 +688,79 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_DWEMPTY));
       }
-      const bool do_row = lane_active && row < rows_real_u && !*abort_flag;
+      const bool do_row = row < rows_real_u && !*abort_flag;
+      const unsigned row_mask = __ballot_sync(0xffffffffu, do_row);      // lanes l and l+16 always agree
       const int64_t l = l0 + row, gl = u.label0 + l;
       const bool sr = u.flags & HASTE_F_SR, packed = u.flags & HASTE_F_RNG_PACKED, contract = u.flags & HASTE_F_CONTRACT;
       // the old bias comes from the group's bias column in shared memory
-      const uint16_t b_old = (has_bias && kh == 0 && lane_active)
+      const uint16_t b_old = (has_bias && kh == 0 && half == 0)
                                  ? *reinterpret_cast<const uint16_t*>(sm + C::OFF_BT + wsu * C::BTILE + (row >> 3) * 256 + (row & 7) * 16)
                                  : uint16_t(0);
       if (do_row) {
         __nv_bfloat16* wrow = u.w + l * F;
-        if (DEBUG) {
-          if (a.dw_dump != nullptr) {
-#pragma unroll
-            for (int x = 0; x < UPS / 2; ++x) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + kh * UPS)[x] = gw[x];
-          }
-        }
 #pragma unroll 1
-        for (int pc = 0; pc < NPC; ++pc) {          // pieces of 16 slots (two Philox calls each in the packed stream)
-          const int s0 = kh * UPS + pc * 16;        // first slot of the piece
-          uint32_t g8[8], w8[8];
+        for (int pc = 0; pc < NPC; ++pc) {          // pieces of 16 slots
+          uint32_t p8[8];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) g8[x] = gw[x];
+          for (int x = 0; x < 8; ++x) p8[x] = gw[x];
 #pragma unroll
           for (int p2 = 1; p2 < NPC; ++p2)       // register select (a dynamic index would put gw in local memory)
             if (p2 == pc) {
 #pragma unroll
-              for (int x = 0; x < 8; ++x) g8[x] = gw[p2 * 8 + x];
+              for (int x = 0; x < 8; ++x) p8[x] = gw[p2 * 8 + x];
             }
+          uint32_t g8[NSL / 2], w8[NSL / 2];
+          if (SPLIT) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const uint32_t up = __shfl_sync(row_mask, p8[4 + x], lane & 15);     // upper 8 slots of the piece, from the lane that read TMEM
+              g8[x] = half ? up : p8[x];
+            }
+          } else {
+#pragma unroll
+            for (int x = 0; x < NSL / 2; ++x) g8[x] = p8[x];
+          }
+          const int s0 = kh * UPS + pc * 16 + half * 8;        // first slot of this lane's part of the piece
           {
-            // 16 old weights = two 16-byte chunks of the row in the W tile
+            // the old weights: one (SPLIT) or two 16-byte chunks of the row in the W tile
             const uint8_t* wsm = sm + C::OFF_W + wsu * WSTAGE + (s0 >> 6) * WBLK + row * 128;
             const int c0 = (s0 & 63) >> 3;
             const uint4 wa = *reinterpret_cast<const uint4*>(wsm + ((c0 ^ (row & 7)) << 4));
-            const uint4 wb = *reinterpret_cast<const uint4*>(wsm + (((c0 + 1) ^ (row & 7)) << 4));
-            w8[0] = wa.x; w8[1] = wa.y; w8[2] = wa.z; w8[3] = wa.w; w8[4] = wb.x; w8[5] = wb.y; w8[6] = wb.z; w8[7] = wb.w;
+            w8[0] = wa.x; w8[1] = wa.y; w8[2] = wa.z; w8[3] = wa.w;
+            if (!SPLIT) {
+              const uint4 wb = *reinterpret_cast<const uint4*>(wsm + (((c0 + 1) ^ (row & 7)) << 4));
+              w8[NSL / 2 - 4] = wb.x; w8[NSL / 2 - 3] = wb.y; w8[NSL / 2 - 2] = wb.z; w8[NSL / 2 - 1] = wb.w;
+            }
           }
-          uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};           // 16 x 16 random bits, two per word
+          if (DEBUG) {
+            if (a.dw_dump != nullptr) {
+#pragma unroll
+              for (int x = 0; x < NSL / 2; ++x) reinterpret_cast<uint32_t*>(a.dw_dump + l * F + s0)[x] = g8[x];
+            }
+          }
+          uint32_t rnd[NSL / 2];           // NSL x 16 random bits, two per word
+#pragma unroll
+          for (int x = 0; x < NSL / 2; ++x) rnd[x] = 0u;
           if (sr) {
             if (packed) {
-              const uint4 rp0 = rand_packed8_call(u.seed, u.step, gl, s0 >> 3), rp1 = rand_packed8_call(u.seed, u.step, gl, (s0 >> 3) + 1);
+              const uint4 rp0 = rand_packed8_call(u.seed, u.step, gl, s0 >> 3);
               rnd[0] = rp0.x; rnd[1] = rp0.y; rnd[2] = rp0.z; rnd[3] = rp0.w;
-              rnd[4] = rp1.x; rnd[5] = rp1.y; rnd[6] = rp1.z; rnd[7] = rp1.w;
+              if (!SPLIT) {
+                const uint4 rp1 = rand_packed8_call(u.seed, u.step, gl, (s0 >> 3) + 1);
+                rnd[NSL / 2 - 4] = rp1.x; rnd[NSL / 2 - 3] = rp1.y; rnd[NSL / 2 - 2] = rp1.z; rnd[NSL / 2 - 1] = rp1.w;
+              }
             } else {
 #pragma unroll
-              for (int x = 0; x < 16; x += 2)
+              for (int x = 0; x < NSL; x += 2)
                 rnd[x >> 1] = rand16_reference_call(u.seed, gl * F + s0 + x) | (rand16_reference_call(u.seed, gl * F + s0 + x + 1) << 16);
             }
           }
-          uint32_t ob[8];
+          uint32_t ob[NSL / 2];
           if (!MOM && sr && contract) {
             // the configuration every benchmark and the reference's compiled kernel use, without per-element flag
             // tests: w' = fma(-lr, fma(wd, w, g), w), then add 16 random bits and keep the high half
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
+            for (int p = 0; p < NSL / 2; ++p) {
               const float g0 = __uint_as_float(g8[p] << 16), g1 = __uint_as_float(g8[p] & 0xFFFF0000u);
               const float w0 = __uint_as_float(w8[p] << 16), w1 = __uint_as_float(w8[p] & 0xFFFF0000u);
               const float n0 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w0, g0), w0), n1 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w1, g1), w1);
@@ -743,17 +769,17 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
               ob[p] = __byte_perm(s0b, s1b, 0x7632);              // high halves: s0b -> low 16 bits, s1b -> high 16 bits
             }
           } else {
-            float mv[16];
+            float mv[NSL];
             float* mrow = MOM ? u.mom_w + l * F + s0 : nullptr;
             if (MOM) {
 #pragma unroll
-              for (int x = 0; x < 4; ++x) {
+              for (int x = 0; x < NSL / 4; ++x) {
                 const float4 m4 = reinterpret_cast<const float4*>(mrow)[x];
                 mv[4 * x] = m4.x; mv[4 * x + 1] = m4.y; mv[4 * x + 2] = m4.z; mv[4 * x + 3] = m4.w;
               }
             }
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
+            for (int p = 0; p < NSL / 2; ++p) {
               const float g0 = __uint_as_float(g8[p] << 16), g1 = __uint_as_float(g8[p] & 0xFFFF0000u);
               const float w0 = __uint_as_float(w8[p] << 16), w1 = __uint_as_float(w8[p] & 0xFFFF0000u);
               float n0, n1;
@@ -766,13 +792,13 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
             }
             if (MOM) {
 #pragma unroll
-              for (int x = 0; x < 4; ++x) reinterpret_cast<float4*>(mrow)[x] = make_float4(mv[4 * x], mv[4 * x + 1], mv[4 * x + 2], mv[4 * x + 3]);
+              for (int x = 0; x < NSL / 4; ++x) reinterpret_cast<float4*>(mrow)[x] = make_float4(mv[4 * x], mv[4 * x + 1], mv[4 * x + 2], mv[4 * x + 3]);
             }
           }
           *reinterpret_cast<uint4*>(wrow + s0) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-          *reinterpret_cast<uint4*>(wrow + s0 + 8) = make_uint4(ob[4], ob[5], ob[6], ob[7]);
+          if (!SPLIT) *reinterpret_cast<uint4*>(wrow + s0 + 8) = make_uint4(ob[NSL / 2 - 4], ob[NSL / 2 - 3], ob[NSL / 2 - 2], ob[NSL / 2 - 1]);
         }
-        if (has_bias && kh == 0) {
+        if (has_bias && kh == 0 && half == 0) {
           if (DEBUG) if (a.db_dump != nullptr) a.db_dump[l] = __float2bfloat16_rn(gb);
           uint32_t r16 = 0;
           if (sr) r16 = rand16_call(u.flags, u.seed ^ (packed ? 0x62696173ull : 0ull), u.step, gl);
