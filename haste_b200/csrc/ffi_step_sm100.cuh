@@ -82,8 +82,8 @@ struct Cfg {
   static_assert(TM_DW + FR <= TM_COLS, "TMEM budget");
 
   static constexpr int N_EA = 8;                      // loss-epilogue warps: 4 TMEM lane quarters x 2 column halves
-  static constexpr int EBS = F;                       // slots per scatter warp
-  static constexpr int N_EB = 4 * (F / EBS);          // scatter warps: one per TMEM lane quarter
+  static constexpr int EBS = 64;                      // slots per scatter warp
+  static constexpr int N_EB = 4 * (F / EBS);          // scatter warps: 4 TMEM lane quarters x 64-slot chunks
   static constexpr int N_UP = 8;                      // update warps: 4 TMEM lane quarters x 2 slot halves
   static constexpr int W_EA = 4, W_EB = W_EA + N_EA, W_UP = W_EB + N_EB;
   static constexpr int NPW = 4;                       // producer warps: warp 0, warp 2, then extra warps after the update warps
