@@ -378,18 +378,22 @@ def _c5_lines(args, rank, world, device, flush, dist):
            "kernel_ms_ranks": [round(k, 4) for k in kern_ranks], "parity_n": parity,
            "workload": f"c5: B={c['B']} D={c['D']} L={c['L']} fan_in={c['F']} G={c['G']} loss={c['loss']}"}
     # one GPU, same process: rank 0 holds the whole layer and uses every SM, the other ranks wait
-    n1 = torch.zeros(1, dtype=torch.float64, device=device)
+    n1 = torch.zeros(2, dtype=torch.float64, device=device)
     if rank == 0:
         from haste_b200 import _lib
         _lib.check(_lib.lib.haste_ffi_set_max_ctas(0), "set_max_ctas")
         _, layer1, _, _ = build_problem("c5", 0, 1, device)
         ms1, _, _ = _time_steps(layer1, dev_batches, max(5, steps // 3), 3, 1, device, flush, dist)
         n1[0] = statistics.median(ms1)
+        n1[1], _ = _time_kernel(layer1.shard, dev_batches[0][0], dev_batches[0][1], device, flush, 5, None, 1)
         del layer1
         torch.cuda.empty_cache()
     dist.all_reduce(n1, op=dist.ReduceOp.MAX)
-    out["n1_ms_per_step"] = float(n1)
-    out["vs_n1"] = float(n1) / out["ms_per_step"]
+    out["n1_ms_per_step"] = float(n1[0])
+    out["vs_n1"] = float(n1[0]) / out["ms_per_step"]
+    # the whole layer's fused kernel on one GPU against the measured bf16 burst peak (same definition as `roofline`)
+    out["n1_kernel_ms"] = float(n1[1])
+    out["n1_roofline_frac"] = 6.0 * c["B"] * c["L"] * c["F"] / (float(n1[1]) * 1e-3) / 1e12 / measured_peaks()["bf16_tflops"]
     return out
 
 
@@ -600,7 +604,7 @@ def run_aux(args):
         ("ffi_forward (unfused, writes Z)", lambda: hffi.forward(loc, xt, W, bias, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_features (unfused, reads dY)", lambda: hffi.backward_features(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
         ("ffi_backward_weights (unfused, reads dY, writes dW)", lambda: hffi.backward_weights(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 4 * NG * F),
-        ("ffi_backward (both gradients, one pass over dY incl. row padding)", lambda: hffi.backward_both(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 2 * L * F + 4 * NG * F),
+        ("ffi_backward (both gradients, one pass over a contiguous [B,L] dY)", lambda: hffi.backward_both(xt, W, loc, dy, G), 2 * B * L + 2 * L * F + 2 * L * F + 4 * NG * F),
         ("ffi_bww_sr_sgd (backward-weights + SGD/SR, no dW)", lambda: hffi.bww_sr_sgd(xt, loc, dy, w2, None, None, None, G, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 2 * B * L + 4 * L * F + 4 * NG * F),
         ("sgd_sr_update packed stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="packed")), 6 * L * F),
         ("sgd_sr_update reference stream", lambda: hffi.sgd_sr_update(w2, g, None, 0, LR, WD, 0.0, SEED, 1, hffi.make_flags(rng="reference")), 6 * L * F),

@@ -127,7 +127,7 @@ int haste_ffi_backward(const void* xt, const void* w, const int32_t* loc, const 
     cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
   }
-  if (backward_sm100_supported(dy, dw, B, F, G, ldy)) return launch_backward_sm100(xt, w, loc, dy, dxt, dw, dbias, B, D, F, L, G, ldy, st);
+  if (backward_sm100_supported(xt, w, dy, dw, B, D, F, L, G)) return launch_backward_sm100(xt, w, loc, dy, dxt, dw, dbias, B, D, F, L, G, ldy, st);
   if (int rc = launch_bwd_features(w, loc, dy, dxt, B, D, F, L, G, ldy, st)) return rc;
   return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, st);
 }

@@ -181,6 +181,10 @@ __global__ void tgt_fill_kernel(const int32_t* __restrict__ coo, int64_t nnz, in
 // the loss scalar; every other block transposes one 32x32 tile of x [B,D] -> xt [D,B] and clears the same tile
 // of dxt [D,B].  Replaces one memset, the three bucketing kernels, the transpose and two fills.
 constexpr int PREP_THREADS = 1024;
+// VEC: B and D are multiples of 8 and the three arrays are 16-byte aligned; a block then moves a 64 (batch) x 128
+// (feature) tile with 16-byte accesses on both sides, so that the whole preparation is a few dozen blocks and still
+// finishes in microseconds when most SMs are held by a persistent kernel of another stream.
+template <bool VEC>
 __global__ void __launch_bounds__(PREP_THREADS) step_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, float* __restrict__ dxt,
                                                                     float* __restrict__ loss, const int32_t* __restrict__ coo, int64_t nnz,
                                                                     int64_t label0, int64_t L, int G, int NG, int32_t* __restrict__ ptr,
@@ -242,8 +246,40 @@ __global__ void __launch_bounds__(PREP_THREADS) step_prepare_kernel(const uint16
     }
     return;
   }
-  __shared__ uint16_t tile[32][34];
   const int blk = blockIdx.x - 1;
+  if (VEC) {
+    // tile [64 batch rows][128 features] in shared memory, 16-byte chunks; the chunk index is XORed with the row's
+    // 8-row group so that the column reads of the transposed write-out spread over the banks
+    __shared__ __align__(16) uint16_t tile[64][128];
+    const int64_t d0 = static_cast<int64_t>(blk % tiles_d) * 128, b0 = static_cast<int64_t>(blk / tiles_d) * 64;
+    {
+      const int row = tid >> 4, ch = tid & 15;
+      const int64_t b = b0 + row, d = d0 + ch * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (b < B && d < D) v = *reinterpret_cast<const uint4*>(x + b * D + d);
+      *reinterpret_cast<uint4*>(&tile[row][(ch ^ ((row >> 3) & 7)) * 8]) = v;
+    }
+    __syncthreads();
+    {
+      const int dl = tid >> 3, b8 = tid & 7;                 // 8 lanes write one 128-byte run of a row of xt
+      const int64_t d = d0 + dl, b = b0 + b8 * 8;
+      if (d < D && b < B) {
+        const int col = (((dl >> 3) ^ b8) << 3) | (dl & 7);  // rows b8*8 .. b8*8+7 all lie in 8-row group b8
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = static_cast<uint32_t>(tile[b8 * 8 + 2 * i][col]) | (static_cast<uint32_t>(tile[b8 * 8 + 2 * i + 1][col]) << 16);
+        *reinterpret_cast<uint4*>(xt + d * B + b) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int idx = tid + k * PREP_THREADS, dl = idx >> 4, c = idx & 15;
+      const int64_t d = d0 + dl, b = b0 + c * 4;
+      if (d < D && b < B) *reinterpret_cast<float4*>(dxt + d * B + b) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
+  __shared__ uint16_t tile[32][34];
   const int64_t d0 = static_cast<int64_t>(blk % tiles_d) * 32, b0 = static_cast<int64_t>(blk / tiles_d) * 32;
   const int tx = tid & 31, ty = tid >> 5;            // 32 x 32 threads: one element each
   {
@@ -264,11 +300,13 @@ int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const 
   const size_t sm = sizeof(int32_t) * static_cast<size_t>(NG);
   if (sm > 200 * 1024) return fail(HASTE_ERR_TOO_LARGE, "haste_ffi_step_prepare: %lld label groups need more shared memory than one block has; "
                                    "use haste_transpose_bf16 + haste_targets_bucket", (long long)NG);
-  cudaError_t e = cudaFuncSetAttribute(step_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
+  const bool vec = (B % 8) == 0 && (D % 8) == 0 && aligned16(x) && aligned16(xt) && aligned16(dxt);
+  auto k = vec ? step_prepare_kernel<true> : step_prepare_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
   if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  const int tiles_d = static_cast<int>((D + 31) / 32), tiles_b = static_cast<int>((B + 31) / 32);
-  step_prepare_kernel<<<1 + tiles_d * tiles_b, PREP_THREADS, sm, st>>>((const uint16_t*)x, (uint16_t*)xt, dxt, loss, coo, nnz, label0, L, int(G), int(NG),
-                                                               ptr, ent, B, D, tiles_d);
+  const int tiles_d = static_cast<int>(vec ? (D + 127) / 128 : (D + 31) / 32), tiles_b = static_cast<int>(vec ? (B + 63) / 64 : (B + 31) / 32);
+  k<<<1 + tiles_d * tiles_b, PREP_THREADS, sm, st>>>((const uint16_t*)x, (uint16_t*)xt, dxt, loss, coo, nnz, label0, L, int(G), int(NG), ptr, ent, B, D,
+                                                     tiles_d);
   return check_launch("step_prepare_kernel");
 }
 

@@ -1,17 +1,26 @@
-// Unfused backward of the FFI layer on tcgen05 / TMEM, group size 128, fan-in 64: one pass over dY [B, ldy]
-// produces both gradients of the autograd surface,
+// Unfused backward of the FFI layer on tcgen05 / TMEM, for the layer shapes (group size 128, fan-in 64) and
+// (group size 64, fan-in 128): one pass over dY [B, ldy] produces both gradients of the autograd surface,
 //     dxt[loc[g,k], b] += sum_{l in g} w[l,k] * dy[b,l]          (fp32, reduced into dxt with red.global.add)
 //     dw [l, k]         = sum_b dy[b,l] * xt[loc[g,k], b]          (bf16, round to nearest)
-//     dbias[l]          = sum_b dy[b,l]                            (bf16; via a row of ones appended to the X tile)
+//     dbias[l]          = sum_b dy[b,l]                            (bf16; via a row of ones under the X tile)
 // so dY is read from HBM once instead of once per gradient.  HBM-bound by that read (2*B*L bytes).
 //
 // Persistent, one CTA per SM.  Same operand layouts as the fused train step: per 128-row batch tile the Y tile
-// (dY slice, now copied in by the producers instead of computed by an epilogue), the X tile and the W tile sit
-// in 128-byte-swizzled shared memory; backward-features takes Y as K-major A and W as MN-major B,
-// backward-weights takes Y as MN-major A and X as K-major B.  Warp roles (672 threads): warps 0, 2 and 16-20 are
-// producers (cp.async; one producer warp per ring stage), warp 1 issues backward-features, warp 3
-// backward-weights, warps 4-11 drain dXg (TMEM -> registers -> coalesced red.global.add.f32), warps 12-15 turn
-// the dW accumulator into bf16 rows of dw / dbias at the end of each group.  Requires 16-byte-aligned dY rows (ldy % 8 == 0).
+// (a dY slice), the X tile and the W tile sit in 128-byte-swizzled shared memory; backward-features takes Y as
+// K-major A and W as MN-major B, backward-weights takes Y as MN-major A and X as K-major B.
+//
+// The rows of dY need no alignment.  An autograd gradient is a contiguous [B, L] tensor and L is odd in most
+// real label sets, so a row's slice for one group starts at any even byte offset.  The eight "Y warps" copy
+// the 16-byte-aligned chunks that cover each row slice (cp.async, G/8 + 1 chunks per row) to the slice's own place
+// in the Y tile, then shift every row left by its misalignment inside shared memory (two 16-byte reads, four
+// funnel shifts, one 16-byte write per chunk) before they hand the tile to the tensor core.  Rows whose index
+// is equal modulo 8 share the misalignment, so each warp takes one such class and the shift is warp-uniform.
+// Columns at and beyond L are zeroed in the same pass (their neighbours in memory belong to the next row).
+//
+// Warp roles (832 threads): warps 0, 2, 24, 25 gather X tiles with TMA tile::gather4 (warp 0 also loads the W tile
+// through a tensor map), warp 1 issues backward-features, warp 3 backward-weights, warps 4-11 drain dXg (TMEM ->
+// registers -> coalesced red.global.add.f32), warps 12-15 turn the dW accumulator into bf16 rows of dw / dbias at
+// the end of each group, warps 16-23 are the Y warps.  All waits are bounded (see mbar_wait).
 #include "common.cuh"
 #include "launchers.h"
 #include "runtime.h"
@@ -21,35 +30,50 @@ namespace haste {
 namespace b100 {
 using namespace sm100;
 
-constexpr int G = 128, F = 64, BT = 128;
-constexpr int FR = F + 16;                    // X block rows: F gathered rows, one row of ones, 15 zero rows
-constexpr int NXS = 4;
-constexpr int XBLK = FR * 128, XSTAGE = 2 * XBLK;   // 20 KB
-constexpr int WSTAGE = G * 128;                     // 16 KB
-constexpr int YBLK = BT * 128, YSTAGE = 2 * YBLK;   // 32 KB
-constexpr int NYS = 3;
-constexpr int OFF_X = 0;
-constexpr int OFF_W = OFF_X + NXS * XSTAGE;
-constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
-constexpr int OFF_LOC = OFF_Y + NYS * YSTAGE;       // int [2][F]
-constexpr int OFF_BAR = OFF_LOC + 2 * F * 4;
-constexpr int OFF_MISC = OFF_BAR + 40 * 8;
-constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
-static_assert(SMEM_BYTES <= 232448, "shared memory budget");
-constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_YFULL = 2 * NXS, B_YEMPTY = B_YFULL + NYS, B_WFULL = B_YEMPTY + NYS,
-              B_WEMPTY = B_WFULL + 2, B_DXFULL = B_WEMPTY + 2, B_DXEMPTY = B_DXFULL + 2, B_DWFULL = B_DXEMPTY + 2,
-              B_DWEMPTY = B_DWFULL + 2, B_LEMPTY = B_DWEMPTY + 2, NBAR = B_LEMPTY + 2;
-static_assert(NBAR <= 40, "barrier space");
-constexpr int N_EB = 8, N_EC = 4;
-constexpr int N_XPROD = 5;                    // producer warps beyond the two among the first four warps
-constexpr int NTHREADS = (4 + N_EB + N_EC + N_XPROD) * 32;
-constexpr uint32_t TM_DX = 0, TM_DW = 128, TM_DW_STRIDE = 80, TM_COLS = 512;
-constexpr long long WAIT_LIMIT = 4000000000ll;
+template <int G_, int F_>
+struct Cfg {
+  static constexpr int G = G_, F = F_, BT = 128;
+  static_assert((G == 128 && F == 64) || (G == 64 && F == 128), "shapes with a tcgen05 backward");
+  static constexpr int FR = F + 16;                   // X block rows: F gathered rows, one row of ones, 15 zero rows
+  static constexpr int NXS = 4;                       // X ring stages
+  static constexpr int NYS = (G == 128) ? 3 : 2;      // dY ring stages
+  static constexpr int NDX = 2;                       // dXg accumulator stages
+  static constexpr int NDW = (F == 64) ? 2 : 1;       // dW accumulator stages
+  static constexpr int XBLK = FR * 128, XSTAGE = 2 * XBLK;
+  static constexpr int NWB = F / 64, WBLK = G * 128, WSTAGE = NWB * WBLK;
+  static constexpr int NYB = G / 64, YBLK = BT * 128, YSTAGE = NYB * YBLK;
+  static constexpr int NCH = G / 8;                   // 16-byte chunks of a row slice
+  static constexpr int YSIDE = BT * 16;               // one more aligned chunk per row (the tail of a misaligned slice)
+  static constexpr int OFF_X = 0;
+  static constexpr int OFF_W = OFF_X + NXS * XSTAGE;
+  static constexpr int OFF_Y = OFF_W + 2 * WSTAGE;
+  static constexpr int OFF_YSIDE = OFF_Y + NYS * YSTAGE;
+  static constexpr int OFF_LOC = OFF_YSIDE + NYS * YSIDE;      // u32 [2][F]: element offset loc * B of each slot's dxt row
+  static constexpr int OFF_LOCR = OFF_LOC + 2 * F * 4;         // int [4][F]: each producer warp's copy of the group's indices
+  static constexpr int OFF_BAR = OFF_LOCR + 4 * F * 4;
+  static constexpr int OFF_MISC = OFF_BAR + 40 * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+  static_assert(XSTAGE % 1024 == 0 && WBLK % 1024 == 0 && YBLK % 1024 == 0, "tile alignment");
+  static constexpr int B_XFULL = 0, B_XEMPTY = NXS, B_YFULL = 2 * NXS, B_YEMPTY = B_YFULL + NYS, B_WFULL = B_YEMPTY + NYS,
+                       B_WEMPTY = B_WFULL + 2, B_DXFULL = B_WEMPTY + 2, B_DXEMPTY = B_DXFULL + NDX, B_DWFULL = B_DXEMPTY + NDX,
+                       B_DWEMPTY = B_DWFULL + NDW, B_LEMPTY = B_DWEMPTY + NDW, B_FIN = B_LEMPTY + 2, NBAR = B_FIN + 2;
+  static_assert(NBAR <= 40, "barrier space");
+  static constexpr int N_EB = 8;                      // scatter warps: 4 TMEM lane quarters x 2 slot halves
+  static constexpr int EBS = F / 2;                   // slots per scatter warp
+  static constexpr int N_EC = 4;                      // dW writer warps: one per TMEM lane quarter
+  static constexpr int N_Y = 8;                       // Y warps: one per row class (row index modulo 8)
+  static constexpr int NPW = 4;                       // X producer warps: 0, 2 and two after the Y warps
+  static_assert(NPW <= NXS, "a producer must not run more than one phase ahead on any stage barrier");
+  static constexpr int W_EB = 4, W_EC = W_EB + N_EB, W_Y = W_EC + N_EC, W_XP = W_Y + N_Y;
+  static constexpr int NTHREADS = (W_XP + NPW - 2) * 32;
+  static constexpr uint32_t TM_DX = 0, TM_DW = NDX * F, TM_COLS = 512;
+  static_assert(TM_DW + NDW * FR <= TM_COLS, "TMEM budget");
+  static constexpr int ROWS_PER_Q = G / 4;            // label rows of the dW accumulator in one TMEM lane quarter
+};
 
 struct BwdArgs {
   const int32_t* loc;
-  const __nv_bfloat16* xt;
-  const __nv_bfloat16* w;
   const __nv_bfloat16* dy;
   float* dxt;
   __nv_bfloat16* dw;
@@ -57,6 +81,7 @@ struct BwdArgs {
   int* err;
   int64_t B, L, ldy;
   int D, NG;
+  long long wait_limit;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -64,38 +89,45 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs a) {
+template <int G_, int F_>
+__global__ void __launch_bounds__(Cfg<G_, F_>::NTHREADS, 1)
+ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w) {
+  using C = Cfg<G_, F_>;
+  constexpr int G = C::G, F = C::F, BT = C::BT, FR = C::FR, NXS = C::NXS, NYS = C::NYS, NDX = C::NDX, NDW = C::NDW;
+  constexpr int XBLK = C::XBLK, XSTAGE = C::XSTAGE, WBLK = C::WBLK, WSTAGE = C::WSTAGE, YBLK = C::YBLK, YSTAGE = C::YSTAGE, NCH = C::NCH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(sm);
-  int* loc_s = reinterpret_cast<int*>(sm + OFF_LOC);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 8);
-  auto bar = [&](int i) { return sbase + OFF_BAR + i * 8; };
+  uint32_t* loc_s = reinterpret_cast<uint32_t*>(sm + C::OFF_LOC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + C::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::OFF_MISC + 8);
+  auto bar = [&](int i) { return sbase + C::OFF_BAR + i * 8; };
+  const long long WL = a.wait_limit;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = static_cast<int>((a.B + BT - 1) / BT);
 
   if (tid == 0) {
-    for (int i = 0; i < NXS; ++i) { mbar_init(bar(B_XFULL + i), 1); mbar_init(bar(B_XEMPTY + i), 1); }
-    for (int i = 0; i < NYS; ++i) { mbar_init(bar(B_YFULL + i), 1); mbar_init(bar(B_YEMPTY + i), 2); }   // both issuers commit
+    for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 1); mbar_init(bar(C::B_XEMPTY + i), 1); }
+    for (int i = 0; i < NYS; ++i) { mbar_init(bar(C::B_YFULL + i), C::N_Y); mbar_init(bar(C::B_YEMPTY + i), 2); }   // both issuers commit
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(B_WFULL + i), 1);  mbar_init(bar(B_WEMPTY + i), 1);
-      mbar_init(bar(B_DXFULL + i), 1); mbar_init(bar(B_DXEMPTY + i), N_EB);
-      mbar_init(bar(B_DWFULL + i), 1); mbar_init(bar(B_DWEMPTY + i), N_EC);
-      mbar_init(bar(B_LEMPTY + i), N_EB);        // the scatter warps are done with the group's index row
+      mbar_init(bar(C::B_WFULL + i), 1);  mbar_init(bar(C::B_WEMPTY + i), 1);
+      mbar_init(bar(C::B_LEMPTY + i), C::N_EB);      // the scatter warps are done with the group's index row
+      mbar_init(bar(C::B_FIN + i), 1);
     }
+    for (int i = 0; i < NDX; ++i) { mbar_init(bar(C::B_DXFULL + i), 1); mbar_init(bar(C::B_DXEMPTY + i), C::N_EB); }
+    for (int i = 0; i < NDW; ++i) { mbar_init(bar(C::B_DWFULL + i), 1); mbar_init(bar(C::B_DWEMPTY + i), C::N_EC); }
     mbar_fence_init();
     *abort_flag = 0;
   }
   // rows F..FR-1 of every X block: row F = ones (bias-gradient column), the rest zeros; written once
-  for (int i = tid; i < NXS * 2 * 16 * 8; i += NTHREADS) {
+  for (int i = tid; i < NXS * 2 * 16 * 8; i += C::NTHREADS) {
     const int chunk = i & 7, row = (i >> 3) & 15, blk = i >> 7;
     const uint32_t v = (row == 0) ? 0x3F803F80u : 0u;
-    *reinterpret_cast<uint4*>(sm + OFF_X + blk * XBLK + (F + row) * 128 + chunk * 16) = make_uint4(v, v, v, v);
+    *reinterpret_cast<uint4*>(sm + C::OFF_X + blk * XBLK + (F + row) * 128 + chunk * 16) = make_uint4(v, v, v, v);
   }
   fence_proxy_async();
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    tmem_alloc(smem_u32(tmem_slot), C::TM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -103,255 +135,373 @@ __global__ void __launch_bounds__(NTHREADS, 1) ffi_backward_sm100_kernel(BwdArgs
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_my_groups = (a.NG > static_cast<int>(blockIdx.x)) ? (a.NG - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+  auto group_of = [&](int gi) { return static_cast<int>(blockIdx.x) + gi * static_cast<int>(gridDim.x); };
 
-  if (warp == 0 || warp == 2 || warp >= 4 + N_EB + N_EC) {
-    // ================================================================ producers
-    // Each producer warp has one item in flight at a time and pays the full memory latency for it (dY tiles come
-    // from HBM), so the load rate is the number of producer warps over that latency.  Every ring stage has its
-    // own producer warp — NYS warps for the dY ring, NXS for the X ring, the first X warp also loads the W tiles —
-    // so one warp sees all phases of its stage's barriers in order (a producer dealt arbitrary items could run a
-    // full ring ahead of a slower one and mistake an old phase of the one-bit parity for the one it waits for).
-    static_assert(2 + N_XPROD == NXS + NYS, "one producer warp per ring stage");
-    const int p = warp < 4 ? (warp >> 1) : 2 + warp - (4 + N_EB + N_EC);
-    const bool y_prod = p < NYS;
-    const int my_stage = y_prod ? p : p - NYS;
-    const bool w_prod = p == NYS;
-    int it = 0;
-    auto land = [&](uint32_t full_bar) {
-      cp_async_commit();
-      cp_async_wait<0>();
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_bar);
-    };
+  const int prod_id = warp == 0 ? 0 : (warp == 2 ? 1 : (warp >= C::W_XP ? 2 + warp - C::W_XP : -1));
+  if (prod_id >= 0) {
+    // ================================================================ X / W producers
+    // Per group: producer 0 writes the index row (as dxt row offsets for the scatter warps) and loads the W tile
+    // through the tensor map.  Per batch tile: F index rows of xt, 256 bytes each, as TMA gather4 loads (four index
+    // rows per instruction, landing at their swizzled positions), dealt round-robin over the four warps.
+    int it = 0, w_armed = 0, my_last = -1;
     for (int gi = 0; gi < n_my_groups; ++gi) {
-      const int g = blockIdx.x + gi * gridDim.x;
+      const int g = group_of(gi);
       const int ws = gi & 1;
       const int64_t l0 = static_cast<int64_t>(g) * G;
-      const int rows_real = static_cast<int>(imin64(G, a.L - l0));
       const int32_t* lrow = a.loc + static_cast<int64_t>(g) * F;
-      const int loc_lo = min(max(__ldg(lrow + lane), 0), a.D - 1);
-      const int loc_hi = min(max(__ldg(lrow + lane + 32), 0), a.D - 1);
-      if (w_prod) {
-        mbar_wait(bar(B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WAIT_LIMIT, 100);
-        mbar_wait(bar(B_LEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WAIT_LIMIT, 100);
+      int locv[F / 32];
+#pragma unroll
+      for (int j = 0; j < F / 32; ++j) locv[j] = min(max(__ldg(lrow + lane + 32 * j), 0), a.D - 1);   // clamped: never addresses outside xt / dxt
+      if (prod_id == 0) {
+        bool ok = mbar_wait(bar(C::B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WL, 100);
+        ok = mbar_wait(bar(C::B_LEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WL, 100) && ok;
         __syncwarp();
-        loc_s[ws * F + lane] = loc_lo;
-        loc_s[ws * F + lane + 32] = loc_hi;
-        const uint32_t wb = sbase + OFF_W + ws * WSTAGE;
-#pragma unroll 4
-        for (int i = 0; i < 32; ++i) {
-          const int idx = i * 32 + lane, r = idx >> 3, c = idx & 7;
-          cp_async16(wb + r * 128 + ((c ^ (r & 7)) << 4), a.w + (l0 + r) * F + c * 8, r < rows_real);
+#pragma unroll
+        for (int j = 0; j < F / 32; ++j)
+          loc_s[ws * F + lane + 32 * j] = static_cast<uint32_t>(locv[j]) * static_cast<uint32_t>(a.B);   // D * B < 2^32 is a launch condition
+        __syncwarp();
+        if (ok && !*abort_flag) {
+          if (lane == 0) {
+            // the arrival also releases the index row written above to the warps that wait for this barrier
+            mbar_arrive_expect_tx(bar(C::B_WFULL + ws), WSTAGE);
+#pragma unroll
+            for (int kb = 0; kb < C::NWB; ++kb)
+              tma_load_2d(sbase + C::OFF_W + ws * WSTAGE + kb * WBLK, &tm_w, kb * 64, static_cast<int>(l0), bar(C::B_WFULL + ws));
+          }
+          ++w_armed;
         }
-        land(bar(B_WFULL + ws));
+        __syncwarp();
       }
+      int* locr = reinterpret_cast<int*>(sm + C::OFF_LOCR) + prod_id * F;
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < F / 32; ++j) locr[lane + 32 * j] = locv[j];
+      __syncwarp();
+      const int4* lr4 = reinterpret_cast<const int4*>(locr);
       for (int t = 0; t < T; ++t, ++it) {
-        const int64_t b0 = static_cast<int64_t>(t) * BT;
-        if (!y_prod && it % NXS == my_stage) {            // ---- X item
-          const int xs = it % NXS;
-          mbar_wait(bar(B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 32, WAIT_LIMIT, 100);
-          __syncwarp();
-          const uint32_t xb = sbase + OFF_X + xs * XSTAGE;
-          const int j = lane & 15;
-          const bool valid = b0 + j * 8 < a.B;
-          const uint32_t dcol = (j >> 3) * XBLK + ((j & 7) << 4);
-#pragma unroll 4
-          for (int i = 0; i < 32; ++i) {
-            const int k = i * 2 + (lane >> 4);
-            const int lk = __shfl_sync(0xffffffffu, (i < 16) ? loc_lo : loc_hi, k & 31);
-            const __nv_bfloat16* src = a.xt + static_cast<int64_t>(lk) * a.B + b0 + j * 8;
-            cp_async16(xb + ((dcol + k * 128) ^ ((k & 7) << 4)), valid ? src : a.xt, valid);
-          }
-          land(bar(B_XFULL + xs));
+        if (it % C::NPW != prod_id) continue;
+        const int xs = it % NXS;
+        const bool okx = mbar_wait(bar(C::B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 32, WL, 100);
+        __syncwarp();
+        if (!okx || *abort_flag) continue;
+        const int b0 = t * BT;
+        const uint32_t xb = sbase + C::OFF_X + xs * XSTAGE;
+        if (lane == 0) mbar_arrive_expect_tx(bar(C::B_XFULL + xs), F * 256);
+        __syncwarp();
+#pragma unroll
+        for (int i = lane; i < 2 * (F / 4); i += 32) {
+          const int blk = i / (F / 4), r4 = i % (F / 4);
+          const int4 lr = lr4[r4];
+          tma_gather4(xb + blk * XBLK + r4 * 512, &tm_x, b0 + blk * 64, lr.x, lr.y, lr.z, lr.w, bar(C::B_XFULL + xs));
         }
-        if (y_prod && it % NYS == my_stage) {            // ---- Y item: dy[b0 .. b0+127, l0 .. l0+127] -> two 64-label blocks
-          const int ys = it % NYS;
-          mbar_wait(bar(B_YEMPTY + ys), ((it / NYS) & 1) ^ 1, abort_flag, a.err, 33, WAIT_LIMIT, 100);
-          __syncwarp();
-          const uint32_t yb = sbase + OFF_Y + ys * YSTAGE;
-          const int c16 = lane & 15;                          // 16-byte chunk (8 labels) inside the 128-label row
-          const int64_t col = l0 + c16 * 8;
-          const bool cvalid = col + 8 <= a.ldy;             // columns L..ldy-1 of dy are zero by contract; past ldy: zero fill
-          const uint32_t dcol = (c16 >> 3) * YBLK + ((c16 & 7) << 4);
-#pragma unroll 4
-          for (int i = 0; i < 64; ++i) {
-            const int r = i * 2 + (lane >> 4);
-            const bool valid = cvalid && (b0 + r < a.B);
-            const __nv_bfloat16* src = a.dy + (b0 + r) * a.ldy + col;
-            cp_async16(yb + ((dcol + r * 128) ^ ((r & 7) << 4)), valid ? src : a.dy, valid);
-          }
-          land(bar(B_YFULL + ys));
-        }
+        my_last = it;
       }
     }
+    // every copy this warp started has to land before the CTA may exit (only the most recent use of each stage)
+    for (int j = max(0, it - NXS); j < it; ++j)
+      if (j % C::NPW == prod_id && j <= my_last) mbar_wait_final(bar(C::B_XFULL + j % NXS), (j / NXS) & 1, WL);
+    for (int j = max(0, w_armed - 2); j < w_armed; ++j) mbar_wait_final(bar(C::B_WFULL + (j & 1)), (j >> 1) & 1, WL);
+  } else if (warp >= C::W_Y && warp < C::W_XP) {
+    // ================================================================ Y warps: dY slice -> aligned, swizzled Y tile
+    // Warp k owns the rows r = k, k + 8, ... of every tile.  Copies run LAG tiles ahead of the shifting.
+    const int k = warp - C::W_Y;
+    constexpr int LAG = NYS - 1;
+    constexpr int PER_ROW = NCH + 1;
+    constexpr int N_CP = 16 * PER_ROW;                 // copies per warp and tile
+    const uintptr_t dy_base = reinterpret_cast<uintptr_t>(a.dy);
+    const uintptr_t dy_end = dy_base + 2ull * static_cast<uint64_t>((a.B - 1) * a.ldy + a.L);   // first byte after the last gradient
+    const int n_items = n_my_groups * T;
+    const int rr = lane >> 3, c = lane & 7;            // shifting: lane = (row within a set of four, chunk within a 64-label block)
+    int gi_i = 0, t_i = 0;                             // issue position
+    int gi_p = 0, t_p = 0;                             // shift position
+    for (int it = 0; it < n_items + LAG; ++it) {
+      if (it < n_items) {
+        const int ys = it % NYS;
+        const bool ok = mbar_wait(bar(C::B_YEMPTY + ys), ((it / NYS) & 1) ^ 1, abort_flag, a.err, 33, WL, 100);
+        __syncwarp();
+        if (ok && !*abort_flag) {
+          const int64_t l0 = static_cast<int64_t>(group_of(gi_i)) * G;
+          const int64_t b0 = static_cast<int64_t>(t_i) * BT;
+          const uint32_t yb = sbase + C::OFF_Y + ys * YSTAGE, yside = sbase + C::OFF_YSIDE + ys * C::YSIDE;
+#pragma unroll
+          for (int j = 0; j < (N_CP + 31) / 32; ++j) {
+            const int idx = lane + 32 * j;
+            if (idx < N_CP) {
+              const int ri = idx / PER_ROW, ch = idx % PER_ROW;
+              const int r = k + 8 * ri;
+              const int64_t b = b0 + r;
+              const uintptr_t row_addr = dy_base + 2ull * static_cast<uint64_t>(b * a.ldy + l0);
+              const uintptr_t src = (row_addr & ~static_cast<uintptr_t>(15)) + 16u * ch;
+              // a chunk is read when it holds at least one byte of the tensor (it lies in the same 16-byte granule as
+              // that byte); everything else is zero-filled
+              const bool valid = b < a.B && src + 16 > dy_base && src < dy_end && (ch < NCH || (row_addr & 15) != 0);
+              const uint32_t dst = ch < NCH ? yb + (ch >> 3) * YBLK + r * 128 + (((ch & 7) ^ (r & 7)) << 4) : yside + r * 16;
+              cp_async16(dst, valid ? reinterpret_cast<const void*>(src) : reinterpret_cast<const void*>(dy_base & ~static_cast<uintptr_t>(15)), valid);
+            }
+          }
+        }
+        if (++t_i == T) { t_i = 0; ++gi_i; }
+      }
+      cp_async_commit();
+      if (it >= LAG) {
+        cp_async_wait<LAG>();                          // this lane's copies of tile it - LAG have landed
+        __syncwarp();                                  // ... and so have the other lanes'
+        const int jt = it - LAG, ys = jt % NYS;
+        const int64_t l0 = static_cast<int64_t>(group_of(gi_p)) * G;
+        const int64_t b0 = static_cast<int64_t>(t_p) * BT;
+        // all rows of this warp start at the same offset inside a 16-byte granule
+        const uint32_t sh = static_cast<uint32_t>((dy_base + 2ull * static_cast<uint64_t>((b0 + k) * a.ldy + l0)) & 15u);
+        const bool mask_cols = l0 + G > a.L;
+        if ((sh != 0 || mask_cols) && !*abort_flag) {
+          const uint32_t wo = sh >> 2, hb = (sh & 2u) << 3;     // whole words, then 0 or 16 bits
+          uint8_t* yb = sm + C::OFF_Y + ys * YSTAGE;
+          const uint8_t* yside = sm + C::OFF_YSIDE + ys * C::YSIDE;
+#pragma unroll 1
+          for (int set = 0; set < 4; ++set) {
+            const int r = k + 8 * (4 * set + rr);
+#pragma unroll
+            for (int blk = 0; blk < C::NYB; ++blk) {           // ascending: chunk 8 is read (as a neighbour) before it is rewritten
+              const int cj = blk * 8 + c;
+              uint8_t* p = yb + blk * YBLK + r * 128 + ((c ^ (r & 7)) << 4);
+              const uint8_t* pn = (cj + 1 == NCH) ? yside + r * 16
+                                                  : yb + ((cj + 1) >> 3) * YBLK + r * 128 + ((((cj + 1) & 7) ^ (r & 7)) << 4);
+              const uint4 v0 = *reinterpret_cast<const uint4*>(p);
+              const uint4 v1 = *reinterpret_cast<const uint4*>(pn);
+              __syncwarp();                            // every lane has read its neighbour's chunk before anyone rewrites one
+              uint32_t w0, w1, w2, w3, w4;
+              switch (wo) {                            // warp-uniform
+                case 0: w0 = v0.x; w1 = v0.y; w2 = v0.z; w3 = v0.w; w4 = v1.x; break;
+                case 1: w0 = v0.y; w1 = v0.z; w2 = v0.w; w3 = v1.x; w4 = v1.y; break;
+                case 2: w0 = v0.z; w1 = v0.w; w2 = v1.x; w3 = v1.y; w4 = v1.z; break;
+                default: w0 = v0.w; w1 = v1.x; w2 = v1.y; w3 = v1.z; w4 = v1.w; break;
+              }
+              uint4 o = make_uint4(__funnelshift_r(w0, w1, hb), __funnelshift_r(w1, w2, hb), __funnelshift_r(w2, w3, hb),
+                                   __funnelshift_r(w3, w4, hb));
+              if (mask_cols) {
+                const int nv = static_cast<int>(a.L - l0) - 8 * cj;      // valid labels of this chunk
+                if (nv < 8) {
+                  o.x = nv >= 2 ? o.x : (nv == 1 ? (o.x & 0xFFFFu) : 0u);
+                  o.y = nv >= 4 ? o.y : (nv == 3 ? (o.y & 0xFFFFu) : 0u);
+                  o.z = nv >= 6 ? o.z : (nv == 5 ? (o.z & 0xFFFFu) : 0u);
+                  o.w = nv == 7 ? (o.w & 0xFFFFu) : 0u;
+                }
+              }
+              *reinterpret_cast<uint4*>(p) = o;
+            }
+          }
+        }
+        fence_proxy_async();                           // the tile as the tensor core will read it
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_YFULL + ys));
+        if (++t_p == T) { t_p = 0; ++gi_p; }
+      }
+    }
+    cp_async_wait<0>();
   } else if (warp == 1 || warp == 3) {
-    // ================================================================ MMA issuers
-    // Each warp runs its control flow converged; one elected lane issues the products and commits (descriptors
-    // stay in uniform registers this way).
-    {
-      constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
-      constexpr uint32_t ID_BWW = make_idesc(128, FR, 1, 0);
-      const uint64_t D_XB = make_sdesc(sbase + OFF_X, 16, 1024);      // X tile as K-major  B   (backward-weights)
-      const uint64_t D_WM = make_sdesc(sbase + OFF_W, WSTAGE, 1024);  // W tile as MN-major B   (backward-features)
-      const uint64_t D_YA = make_sdesc(sbase + OFF_Y, 16, 1024);      // Y tile as K-major  A   (backward-features)
-      const uint64_t D_YM = make_sdesc(sbase + OFF_Y, YBLK, 1024);    // Y tile as MN-major A   (backward-weights)
-      if (warp == 1) {
-        const uint32_t wm_lo = static_cast<uint32_t>(D_WM), wm_hi = static_cast<uint32_t>(D_WM >> 32);
-        const uint32_t ya_lo = static_cast<uint32_t>(D_YA), ya_hi = static_cast<uint32_t>(D_YA >> 32);
-        const uint32_t id_bwx = ID_BWX;
-        int it = 0, ys = 0, yph = 0;
-        for (int gi = 0; gi < n_my_groups; ++gi) {
-          const int ws = gi & 1;
-          mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 34, WAIT_LIMIT);
-          for (int t = 0; t < T; ++t, ++it) {
-            const int ds = it & 1;
-            mbar_wait(bar(B_YFULL + ys), yph, abort_flag, a.err, 35, WAIT_LIMIT);
-            mbar_wait(bar(B_DXEMPTY + ds), ((it >> 1) & 1) ^ 1, abort_flag, a.err, 36, WAIT_LIMIT);
-            tc_fence_after();
-            const uint32_t ya = ya_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
-            const uint32_t tdx = tmem + TM_DX + (ds ? F : 0);
-            if (elect_one()) {
-              umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
+    // ================================================================ MMA issuers (one elected lane each)
+    constexpr uint32_t ID_BWX = make_idesc(128, F, 0, 1);
+    constexpr uint32_t ID_BWW = make_idesc(G, FR, 1, 0);
+    const uint64_t D_XB = make_sdesc(sbase + C::OFF_X, 16, 1024);      // X tile as K-major  B   (backward-weights)
+    const uint64_t D_WM = make_sdesc(sbase + C::OFF_W, WBLK, 1024);    // W tile as MN-major B   (backward-features)
+    const uint64_t D_YA = make_sdesc(sbase + C::OFF_Y, 16, 1024);      // Y tile as K-major  A   (backward-features)
+    const uint64_t D_YM = make_sdesc(sbase + C::OFF_Y, YBLK, 1024);    // Y tile as MN-major A   (backward-weights)
+    if (warp == 1) {
+      const uint32_t wm_lo = static_cast<uint32_t>(D_WM), wm_hi = static_cast<uint32_t>(D_WM >> 32);
+      const uint32_t ya_lo = static_cast<uint32_t>(D_YA), ya_hi = static_cast<uint32_t>(D_YA >> 32);
+      const uint32_t id_bwx = ID_BWX;
+      int it = 0, ys = 0, yph = 0;
+      for (int gi = 0; gi < n_my_groups; ++gi) {
+        const int ws = gi & 1;
+        const bool okw = mbar_wait(bar(C::B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 34, WL);
+        for (int t = 0; t < T; ++t, ++it) {
+          const int ds = it % NDX;
+          bool ok = mbar_wait(bar(C::B_YFULL + ys), yph, abort_flag, a.err, 35, WL) && okw;
+          ok = mbar_wait(bar(C::B_DXEMPTY + ds), ((it / NDX) & 1) ^ 1, abort_flag, a.err, 36, WL) && ok;
+          tc_fence_after();
+          const uint32_t ya = ya_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), wm = wm_lo + (ws ? (WSTAGE >> 4) : 0u);
+          const uint32_t tdx = tmem + C::TM_DX + ds * F;
+          // dXg[b,k] = sum over label chunks of Y[b, l-chunk] * W[l-chunk, k]
+          if (ok && elect_one()) {
+            umma_bf16_lohi<false>(tdx, ya, ya_hi, wm, wm_hi, id_bwx);
 #pragma unroll
-              for (int ks = 1; ks < G / 16; ++ks)
-                umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
-              tc_commit(bar(B_DXFULL + ds));
-              tc_commit(bar(B_YEMPTY + ys));
-              if (t + 1 == T) tc_commit(bar(B_WEMPTY + ws));
-            }
-            __syncwarp();
-            if (++ys == NYS) { ys = 0; yph ^= 1; }
+            for (int ks = 1; ks < G / 16; ++ks)
+              umma_bf16_lohi<true>(tdx, ya + (((ks >> 2) * YBLK + (ks & 3) * 32) >> 4), ya_hi, wm + ((ks * 2048) >> 4), wm_hi, id_bwx);
+            tc_commit(bar(C::B_DXFULL + ds));
+            tc_commit(bar(C::B_YEMPTY + ys));
+            if (t + 1 == T) tc_commit(bar(C::B_WEMPTY + ws));
           }
-        }
-      } else {
-        const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
-        const uint32_t ym_lo = static_cast<uint32_t>(D_YM), ym_hi = static_cast<uint32_t>(D_YM >> 32);
-        const uint32_t id_bww = ID_BWW;
-        int it = 0, xs = 0, xph = 0, ys = 0, yph = 0;
-        for (int gi = 0; gi < n_my_groups; ++gi) {
-          const uint32_t tdw = tmem + TM_DW + ((gi & 1) ? TM_DW_STRIDE : 0u);
-          mbar_wait(bar(B_DWEMPTY + (gi & 1)), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 37, WAIT_LIMIT);
-          for (int t = 0; t < T; ++t, ++it) {
-            mbar_wait(bar(B_XFULL + xs), xph, abort_flag, a.err, 38, WAIT_LIMIT);
-            mbar_wait(bar(B_YFULL + ys), yph, abort_flag, a.err, 39, WAIT_LIMIT);
-            tc_fence_after();
-            const uint32_t ym = ym_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
-            if (elect_one()) {
-              umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
-#pragma unroll
-              for (int ks = 1; ks < BT / 16; ++ks)
-                umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
-              tc_commit(bar(B_YEMPTY + ys));
-              tc_commit(bar(B_XEMPTY + xs));
-              if (t + 1 == T) tc_commit(bar(B_DWFULL + (gi & 1)));
-            }
-            __syncwarp();
-            if (++xs == NXS) { xs = 0; xph ^= 1; }
-            if (++ys == NYS) { ys = 0; yph ^= 1; }
-          }
+          __syncwarp();
+          if (++ys == NYS) { ys = 0; yph ^= 1; }
         }
       }
+      if (elect_one()) tc_commit(bar(C::B_FIN));
+      __syncwarp();
+      mbar_wait_final(bar(C::B_FIN), 0, WL);
+    } else {
+      const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
+      const uint32_t ym_lo = static_cast<uint32_t>(D_YM), ym_hi = static_cast<uint32_t>(D_YM >> 32);
+      const uint32_t id_bww = ID_BWW;
+      int it = 0, xs = 0, xph = 0, ys = 0, yph = 0;
+      for (int gi = 0; gi < n_my_groups; ++gi) {
+        const int dws = gi % NDW;
+        const uint32_t tdw = tmem + C::TM_DW + dws * FR;
+        const bool okd = mbar_wait(bar(C::B_DWEMPTY + dws), ((gi / NDW) & 1) ^ 1, abort_flag, a.err, 37, WL);
+        for (int t = 0; t < T; ++t, ++it) {
+          bool ok = mbar_wait(bar(C::B_XFULL + xs), xph, abort_flag, a.err, 38, WL) && okd;
+          ok = mbar_wait(bar(C::B_YFULL + ys), yph, abort_flag, a.err, 39, WL) && ok;
+          tc_fence_after();
+          const uint32_t ym = ym_lo + static_cast<uint32_t>(ys) * (YSTAGE >> 4), xb = xb_lo + static_cast<uint32_t>(xs) * (XSTAGE >> 4);
+          // dW[l,k] += sum over batch chunks of Y[b-chunk, l]^T * X[k, b-chunk]
+          if (ok && elect_one()) {
+            umma_bf16_lohi_rt(tdw, ym, ym_hi, xb, xb_hi, id_bww, t > 0);
+#pragma unroll
+            for (int ks = 1; ks < BT / 16; ++ks)
+              umma_bf16_lohi<true>(tdw, ym + ((ks * 2048) >> 4), ym_hi, xb + (((ks >> 2) * XBLK + (ks & 3) * 32) >> 4), xb_hi, id_bww);
+            tc_commit(bar(C::B_YEMPTY + ys));
+            tc_commit(bar(C::B_XEMPTY + xs));
+            if (t + 1 == T) tc_commit(bar(C::B_DWFULL + dws));
+          }
+          __syncwarp();
+          if (++xs == NXS) { xs = 0; xph ^= 1; }
+          if (++ys == NYS) { ys = 0; yph ^= 1; }
+        }
+      }
+      if (elect_one()) tc_commit(bar(C::B_FIN + 1));
+      __syncwarp();
+      mbar_wait_final(bar(C::B_FIN + 1), 0, WL);
     }
-  } else if (warp >= 4 && warp < 4 + N_EB) {
-    // ================================================================ dXg scatter
-    const int q = warp & 3, kh = (warp - 4) >> 2;
-    const int row = q * 32 + lane;
+  } else if (warp >= C::W_EB && warp < C::W_EC) {
+    // ================================================================ scatter: dXg -> dxt
+    const int q = warp & 3, kc = (warp - C::W_EB) >> 2;
+    const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
     int it = 0;
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int ws = gi & 1;
-      mbar_wait(bar(B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 40, WAIT_LIMIT);
-      const int4* loc4 = reinterpret_cast<const int4*>(loc_s + ws * F);
+      mbar_wait(bar(C::B_WFULL + ws), (gi >> 1) & 1, abort_flag, a.err, 40, WL);   // loc_s of this group is in place
+      const uint4* loc4 = reinterpret_cast<const uint4*>(loc_s + ws * F + kc * C::EBS);
       for (int t = 0; t < T; ++t, ++it) {
-        const int64_t b0 = static_cast<int64_t>(t) * BT;
-        const int ds = it & 1;
-        mbar_wait(bar(B_DXFULL + ds), (it >> 1) & 1, abort_flag, a.err, 41, WAIT_LIMIT);
+        const int b0 = t * BT;
+        const int ds = it % NDX;
+        mbar_wait(bar(C::B_DXFULL + ds), (it / NDX) & 1, abort_flag, a.err, 41, WL);
         tc_fence_after();
-        uint32_t r0[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DX + (ds ? F : 0) + kh * 32, r0);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_DXEMPTY + ds));
-        if ((b0 + row < a.B) && !*abort_flag) {
-          float* dbase = a.dxt + b0 + row;
+        const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DX + ds * F + kc * C::EBS;
+        // for a fixed slot the warp's 32 lanes hit 32 consecutive floats of one dxt row: one 128-byte reduction
+        const bool do_red = (b0 + row < a.B) && !*abort_flag;
+        float* dbase = a.dxt + b0 + row;
 #pragma unroll
-          for (int k4 = 0; k4 < 32; k4 += 4) {
-            const int4 lc = loc4[kh * 8 + (k4 >> 2)];
-            atomicAdd(dbase + static_cast<int64_t>(lc.x) * a.B, __uint_as_float(r0[k4 + 0]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.y) * a.B, __uint_as_float(r0[k4 + 1]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.z) * a.B, __uint_as_float(r0[k4 + 2]));
-            atomicAdd(dbase + static_cast<int64_t>(lc.w) * a.B, __uint_as_float(r0[k4 + 3]));
+        for (int half = 0; half < C::EBS / 32; ++half) {
+          uint32_t r0[32];
+          tmem_ld32(ta + half * 32, r0);
+          tmem_ld_wait();
+          if (half == C::EBS / 32 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(C::B_DXEMPTY + ds));
+          }
+          if (do_red) {
+#pragma unroll
+            for (int k4 = 0; k4 < 32; k4 += 4) {
+              const uint4 lc = loc4[half * 8 + (k4 >> 2)];
+              atomicAdd(dbase + lc.x, __uint_as_float(r0[k4 + 0]));
+              atomicAdd(dbase + lc.y, __uint_as_float(r0[k4 + 1]));
+              atomicAdd(dbase + lc.z, __uint_as_float(r0[k4 + 2]));
+              atomicAdd(dbase + lc.w, __uint_as_float(r0[k4 + 3]));
+            }
           }
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_LEMPTY + ws));
+      if (lane == 0) mbar_arrive(bar(C::B_LEMPTY + ws));
     }
-  } else if (warp >= 4 + N_EB && warp < 4 + N_EB + N_EC) {
+  } else if (warp >= C::W_EC && warp < C::W_Y) {
     // ================================================================ dW / dbias rows out of the accumulator
+    // G = 128: TMEM lane == label row.  G = 64: an M = 64 accumulator occupies lanes 0-15 of each lane quarter, so
+    // only the lower half of the warp holds rows (the loads are warp-wide all the same).
     const int q = warp & 3;
-    const int row = q * 32 + lane;                  // label row inside the group == TMEM lane
+    const bool has_row = lane < C::ROWS_PER_Q;
+    const int row = q * C::ROWS_PER_Q + (lane & (C::ROWS_PER_Q - 1));
     for (int gi = 0; gi < n_my_groups; ++gi) {
-      const int g = blockIdx.x + gi * gridDim.x;
+      const int g = group_of(gi);
+      const int dws = gi % NDW;
       const int64_t l0 = static_cast<int64_t>(g) * G;
       const int rows_real = static_cast<int>(imin64(G, a.L - l0));
-      mbar_wait(bar(B_DWFULL + (gi & 1)), (gi >> 1) & 1, abort_flag, a.err, 42, WAIT_LIMIT);
+      mbar_wait(bar(C::B_DWFULL + dws), (gi / NDW) & 1, abort_flag, a.err, 42, WL);
       tc_fence_after();
-      const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + TM_DW + ((gi & 1) ? TM_DW_STRIDE : 0u);
-      uint32_t r0[32], r1[32], rb[8];
-      tmem_ld32(ta, r0);
-      tmem_ld32(ta + 32, r1);
+      const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DW + dws * FR;
+      const bool do_row = has_row && row < rows_real && !*abort_flag;
+      uint4* out = reinterpret_cast<uint4*>(a.dw + (l0 + row) * F);
+#pragma unroll
+      for (int pc = 0; pc < F / 32; ++pc) {
+        uint32_t r0[32];
+        __syncwarp();
+        tmem_ld32(ta + pc * 32, r0);
+        tmem_ld_wait();
+        if (do_row) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            out[pc * 4 + c4] = make_uint4(pack2(__uint_as_float(r0[8 * c4]), __uint_as_float(r0[8 * c4 + 1])),
+                                          pack2(__uint_as_float(r0[8 * c4 + 2]), __uint_as_float(r0[8 * c4 + 3])),
+                                          pack2(__uint_as_float(r0[8 * c4 + 4]), __uint_as_float(r0[8 * c4 + 5])),
+                                          pack2(__uint_as_float(r0[8 * c4 + 6]), __uint_as_float(r0[8 * c4 + 7])));
+        }
+      }
+      uint32_t rb[8];
+      __syncwarp();
       tmem_ld8(ta + F, rb);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DWEMPTY + (gi & 1)));
-      if (row < rows_real && !*abort_flag) {
-        uint4* out = reinterpret_cast<uint4*>(a.dw + (l0 + row) * F);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          out[c] = make_uint4(pack2(__uint_as_float(r0[8 * c]), __uint_as_float(r0[8 * c + 1])), pack2(__uint_as_float(r0[8 * c + 2]), __uint_as_float(r0[8 * c + 3])),
-                              pack2(__uint_as_float(r0[8 * c + 4]), __uint_as_float(r0[8 * c + 5])), pack2(__uint_as_float(r0[8 * c + 6]), __uint_as_float(r0[8 * c + 7])));
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          out[4 + c] = make_uint4(pack2(__uint_as_float(r1[8 * c]), __uint_as_float(r1[8 * c + 1])), pack2(__uint_as_float(r1[8 * c + 2]), __uint_as_float(r1[8 * c + 3])),
-                                  pack2(__uint_as_float(r1[8 * c + 4]), __uint_as_float(r1[8 * c + 5])), pack2(__uint_as_float(r1[8 * c + 6]), __uint_as_float(r1[8 * c + 7])));
-        if (a.dbias != nullptr) a.dbias[l0 + row] = __float2bfloat16_rn(__uint_as_float(rb[0]));
-      }
+      if (lane == 0) mbar_arrive(bar(C::B_DWEMPTY + dws));
+      if (do_row && a.dbias != nullptr) a.dbias[l0 + row] = __float2bfloat16_rn(__uint_as_float(rb[0]));
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, TM_COLS);
+  if (warp == 1) tmem_dealloc(tmem, C::TM_COLS);
 }
 
-}  // namespace b100
-
-bool backward_sm100_supported(const void* dy, const void* dw, int64_t B, int64_t F, int64_t G, int64_t ldy) {
-  return G == b100::G && F == b100::F && (B % 8) == 0 && (ldy % 8) == 0 && aligned16(dy) && aligned16(dw);
-}
-
-int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
-                          int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st) {
-  using namespace b100;
+template <int G_, int F_>
+static int launch_shape(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
+                        int64_t D, int64_t L, int64_t ldy, cudaStream_t st) {
+  using C = Cfg<G_, F_>;
   if (int rc = report_pending_status("tcgen05 backward")) return rc;
   int* err_dev = nullptr;
   if (int rc = device_status_word(&err_dev)) return rc;
   BwdArgs a;
-  a.loc = loc; a.xt = static_cast<const __nv_bfloat16*>(xt); a.w = static_cast<const __nv_bfloat16*>(w);
-  a.dy = static_cast<const __nv_bfloat16*>(dy); a.dxt = dxt; a.dw = static_cast<__nv_bfloat16*>(dw);
+  a.loc = loc; a.dy = static_cast<const __nv_bfloat16*>(dy); a.dxt = dxt; a.dw = static_cast<__nv_bfloat16*>(dw);
   a.dbias = static_cast<__nv_bfloat16*>(dbias); a.err = err_dev;
-  a.B = B; a.L = L; a.ldy = ldy; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + G - 1) / G);
+  a.B = B; a.L = L; a.ldy = ldy; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + C::G - 1) / C::G);
+  a.wait_limit = wait_limit_cycles();
+  CUtensorMap tm_x, tm_w;
+  if (int rc = make_tmap_bf16_2d(&tm_x, xt, static_cast<uint64_t>(B), static_cast<uint64_t>(D), static_cast<uint64_t>(B) * 2, 64, 1)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tm_w, w, static_cast<uint64_t>(C::F), static_cast<uint64_t>(L), static_cast<uint64_t>(C::F) * 2, 64, C::G)) return rc;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = a.NG < sms ? a.NG : sms;
-  cudaError_t e = cudaFuncSetAttribute(ffi_backward_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  auto k = ffi_backward_sm100_kernel<G_, F_>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  ffi_backward_sm100_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
+  k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, tm_x, tm_w);
   return check_launch("ffi_backward_sm100_kernel");
+}
+
+}  // namespace b100
+
+bool backward_sm100_supported(const void* xt, const void* w, const void* dy, const void* dw, int64_t B, int64_t D, int64_t F, int64_t L,
+                              int64_t G) {
+  // tensor maps need 16-byte aligned bases and row strides; dxt row offsets and tile coordinates are 32-bit; dy only
+  // needs its natural 2-byte alignment
+  return ((G == 128 && F == 64) || (G == 64 && F == 128)) && (B % 8) == 0 && aligned16(xt) && aligned16(w) && aligned16(dw) &&
+         (reinterpret_cast<uintptr_t>(dy) & 1u) == 0 && D * B < (int64_t(1) << 32) && L < (int64_t(1) << 31) && B < (int64_t(1) << 31);
+}
+
+int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
+                          int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st) {
+  if (G == 128 && F == 64) return b100::launch_shape<128, 64>(xt, w, loc, dy, dxt, dw, dbias, B, D, L, ldy, st);
+  if (G == 64 && F == 128) return b100::launch_shape<64, 128>(xt, w, loc, dy, dxt, dw, dbias, B, D, L, ldy, st);
+  return fail(HASTE_ERR_UNSUPPORTED, "tcgen05 backward: no kernel for group size %lld, fan-in %lld", (long long)G, (long long)F);
 }
 
 }  // namespace haste

@@ -513,7 +513,7 @@ static int set_smem(K kernel, size_t bytes) {
 int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
                    int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st) {
   // Shape dispatch: the tcgen05 kernel where its tile shapes apply, the warp-mma kernel otherwise
-  if (forward_sm100_supported(z, B, F, G, ldz)) return launch_forward_sm100(loc, xt, w, bias, z, B, D, F, L, G, ldz, zw, st);
+  if (zw >= 8 && forward_sm100_supported(z, xt, w, B, F, L, G, ldz)) return launch_forward_sm100(loc, xt, w, bias, z, B, D, F, L, G, ldz, zw, st);
   const int64_t NG = (L + G - 1) / G;
   dim3 grid(static_cast<unsigned>(NG), static_cast<unsigned>((B + BT - 1) / BT));
   const size_t sm = fwd_smem(int(G), int(F));

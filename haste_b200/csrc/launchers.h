@@ -21,7 +21,7 @@ struct UpdateArgs {
 // zw: writable width of a row of z, L <= zw <= ldz (columns L..zw-1 receive zeros)
 int launch_forward(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
                    int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st);
-bool forward_sm100_supported(const void* z, int64_t B, int64_t F, int64_t G, int64_t ldz);
+bool forward_sm100_supported(const void* z, const void* xt, const void* w, int64_t B, int64_t F, int64_t L, int64_t G, int64_t ldz);
 int launch_forward_sm100(const int32_t* loc, const void* xt, const void* w, const void* bias, void* z, int64_t B, int64_t D, int64_t F,
                          int64_t L, int64_t G, int64_t ldz, int64_t zw, cudaStream_t st);
 int launch_bwd_features(const void* w, const int32_t* loc, const void* dy, float* dxt, int64_t B, int64_t D, int64_t F, int64_t L,
@@ -61,7 +61,8 @@ int launch_targets_bucket_noalloc(const int32_t* coo, int64_t nnz, int64_t label
                                   cudaStream_t st);
 int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const int32_t* coo, int64_t nnz, int64_t label0, int64_t L,
                         int64_t G, int32_t* ptr, uint32_t* ent, int64_t B, int64_t D, cudaStream_t st);
-bool backward_sm100_supported(const void* dy, const void* dw, int64_t B, int64_t F, int64_t G, int64_t ldy);
+bool backward_sm100_supported(const void* xt, const void* w, const void* dy, const void* dw, int64_t B, int64_t D, int64_t F, int64_t L,
+                              int64_t G);
 int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
                           int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st);
 int launch_pad_rows(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols, cudaStream_t st);

@@ -1,5 +1,5 @@
 // sm_100a primitives in inline PTX: mbarrier with bounded waits, TMA loads (tiled and tile::gather4, never
-// multicast), tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
+// multicast) and tiled stores, tcgen05 (alloc / mma / commit / ld), UMMA shared-memory and instruction descriptors, cp.async with
 // zero fill, bulk reduce-add to global.
 #pragma once
 #include <cuda_runtime.h>
@@ -103,6 +103,13 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int 
       "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
       "l"(tmap), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
       : "memory");
+}
+
+// Tiled 2-D store of one box from shared memory (written in the tensor map's swizzle) to element coordinates
+// (x, y); the part of the box outside the tensor is not written.  Completion is tracked by bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(x), "r"(y), "r"(src)
+               : "memory");
 }
 
 // ---------------------------------------------------------------- cp.async (16 B, zero fill when !valid)

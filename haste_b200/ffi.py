@@ -121,12 +121,6 @@ def backward_both(xt, w, loc, dy, G, want_dbias=True):
     dy, ldy = _rows(dy, L)
     dev = xt.device
     with torch.cuda.device(dev):
-        if G == 128 and F == 64 and B % 8 == 0 and (ldy % 8 != 0 or dy.data_ptr() % 16 != 0):
-            # give the rows 16-byte alignment (one extra pass over dy, still cheaper than reading it twice unaligned)
-            ldp = (L + 7) // 8 * 8
-            padded = torch.empty(B, ldp, dtype=torch.bfloat16, device=dev)
-            check(lib.haste_pad_rows_bf16(_ptr(dy), ldy, _ptr(padded), ldp, B, L, _stream(xt)), "pad_rows_bf16")
-            dy, ldy = padded, ldp
         dxt = torch.empty(D, B, dtype=torch.float32, device=dev)
         dw = torch.empty(L, F, dtype=torch.bfloat16, device=dev)
         db = torch.empty(L, dtype=torch.bfloat16, device=dev) if want_dbias else None

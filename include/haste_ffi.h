@@ -88,17 +88,19 @@ int haste_ffi_backward_weights(const void* xt, const int32_t* loc, const void* d
                                haste_stream_t stream);
 
 /* Both gradients of the autograd backward from one pass over dy: dxt as haste_ffi_backward_features, dw / dbias
- * as haste_ffi_backward_weights (dbias may be NULL).  When dy rows are 16-byte aligned (ldy % 8 == 0, aligned
- * base; columns L..ldy-1 must hold zeros) and G=128, F=64, B % 8 == 0, one tcgen05 kernel reads dy once;
- * otherwise the two warp-mma kernels run back to back.  flags: HASTE_F_ZERO_DXT.
+ * as haste_ffi_backward_weights (dbias may be NULL).  For (G=128, F=64) and (G=64, F=128) with B % 8 == 0 one
+ * tcgen05 kernel reads dy once; its rows need no alignment beyond that of a bf16 (a contiguous [B, L] gradient
+ * with odd L is read in place) and whatever lies in columns L..ldy-1 is ignored.  Otherwise the two warp-mma
+ * kernels run back to back.  flags: HASTE_F_ZERO_DXT.
  * Replaces the pair of calls at shared_ffi/bindings.py:44 and :52. */
 int haste_ffi_backward(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias,
                        int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, uint32_t flags,
                        haste_stream_t stream);
 
 /* Copy a bf16 [rows, cols] matrix (row stride ld_src) into [rows, ld_dst] with zeros in columns cols..ld_dst-1
- * (ld_dst % 8 == 0, dst 16-byte aligned): gives gradient rows the alignment haste_ffi_backward's fast path needs
- * (the reference calls grad_output.contiguous() at shared_ffi/bindings.py:37). */
+ * (ld_dst % 8 == 0, dst 16-byte aligned): a utility for callers that want 16-byte aligned gradient rows (no
+ * entry point of this library needs them; the reference calls grad_output.contiguous() at
+ * shared_ffi/bindings.py:37). */
 int haste_pad_rows_bf16(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols,
                         haste_stream_t stream);
 

@@ -92,6 +92,58 @@ def test_forward(hb, shape):
     _assert_close(z2, fo.forward(inp["loc"], inp["X"], inp["W"], None, G, round_bf16=False), what="forward nobias")
 
 
+@pytest.mark.parametrize("shape", [(384, 512, 128 * 300 + 5, 64, 128), (264, 1024, 64 * 400 + 3, 128, 64)])
+def test_forward_many_groups(hb, shape):
+    """More label groups than SMs and several batch tiles per group, so that every ring of the persistent tcgen05
+    forward wraps several times; ragged last group and ragged last batch tile; also into a column block of a
+    wider buffer, where nothing outside the block may change."""
+    ffi, _ = hb
+    B, D, L, F, G = shape
+    inp, dev = _inputs(*shape)
+    want = fo.forward(inp["loc"], inp["X"], inp["W"], inp["bias"], G, round_bf16=False)
+    z = ffi.forward(dev["loc"], dev["Xt"], dev["W"], dev["bias"], G)
+    _assert_close(z, want, what="forward")
+    ldz = (L + 7) // 8 * 8
+    assert (torch.as_strided(z, (B, ldz), (ldz, 1))[:, L:] == 0).all()
+    out = torch.full((B, (L + 31) // 8 * 8), 7.0, dtype=torch.bfloat16, device="cuda")     # row stride a multiple of 16 bytes
+    ffi.forward_into(dev["loc"], dev["Xt"], dev["W"], dev["bias"], G, out, 16)
+    assert torch.equal(out[:, 16:16 + L], z)
+    assert (out[:, :16] == 7).all() and (out[:, 16 + L:] == 7).all()
+
+
+@pytest.mark.parametrize("shape", [(384, 512, 128 * 300 + 5, 64, 128), (264, 1024, 64 * 400 + 3, 128, 64),
+                                   (200, 256, 128 * 9 + 70, 64, 128), (136, 256, 64 * 11 + 6, 128, 64)])
+def test_backward_one_pass_unaligned_rows(hb, shape):
+    """The one-pass tcgen05 backward reads gradient rows at any 2-byte alignment: contiguous [B, L] with odd L (every
+    row starts at a different offset inside a 16-byte granule), a column slice of a wider buffer that starts at an odd
+    column, and aligned rows.  The memory right of every row's L columns holds NaN: nothing of it may leak into a
+    result (the last group's tile covers columns beyond L)."""
+    ffi, _ = hb
+    B, D, L, F, G = shape
+    inp, dev = _inputs(*shape)
+    g = torch.Generator().manual_seed(5)
+    dY = (torch.randn(B, L, generator=g) * 0.5).to(torch.bfloat16)
+    want_x = fo.backward_features(inp["loc"], inp["W"], dY, G, D)
+    want_w = fo.backward_weights(inp["loc"], inp["X"], dY, G, L, round_bf16=False)
+    variants = {"contiguous": dY.cuda()}
+    for name, (left, width) in {"odd column offset": (3, L + 3 + 6), "aligned rows": (8, (L + 8 + 15) // 8 * 8),
+                                "even column offset": (2, L + 2 + 4)}.items():
+        buf = torch.full((B, width), float("nan"), dtype=torch.bfloat16, device="cuda")
+        buf[:, left:left + L] = dY.cuda()
+        variants[name] = buf[:, left:left + L]
+    results = {}
+    for name, dy_dev in variants.items():
+        dxt, dw, db = ffi.backward_both(dev["Xt"], dev["W"], dev["loc"], dy_dev, G)
+        assert torch.isfinite(dxt).all() and torch.isfinite(dw.float()).all() and torch.isfinite(db.float()).all(), name
+        _assert_close(dxt, want_x, rel=1e-2, abs_=1e-3 * max(1.0, float(want_x.abs().max())), what=f"dXt ({name})")
+        _assert_close(dw, want_w, rel=1e-2, abs_=1e-3 * max(1.0, float(want_w.abs().max())), what=f"dW ({name})")
+        _assert_close(db, dY.float().sum(0), rel=1e-2, abs_=2e-2, what=f"dbias ({name})")
+        results[name] = (dw, db)
+    # the weight and bias gradients do not depend on where the rows lie in memory (dxt is reduced with atomics)
+    for name, (dw, db) in results.items():
+        assert torch.equal(dw, results["contiguous"][0]) and torch.equal(db, results["contiguous"][1]), name
+
+
 @pytest.mark.parametrize("shape", SHAPES)
 def test_backward_features_and_weights(hb, shape):
     ffi, _ = hb
@@ -453,10 +505,12 @@ def test_error_convention(hb):
     ffi.check_locations(dev["loc"], 64)
 
 
-def test_step_prepare(hb):
-    """The one-launch preparation equals transpose + clears + haste_targets_bucket."""
+@pytest.mark.parametrize("B,D", [(200, 96), (203, 90), (520, 776), (64, 128)])
+def test_step_prepare(hb, B, D):
+    """The one-launch preparation equals transpose + clears + haste_targets_bucket, on its 16-byte path (B and D
+    multiples of 8; ragged 64 x 128 tiles) and on the element-wise one."""
     ffi, _ = hb
-    B, D, L, G = 200, 96, 5000, 64
+    L, G = 5000, 64
     inp = fo.make_inputs(B, D, L, 16, G, 12, 1.1, seed=9)
     x, coo = inp["X"].cuda(), inp["targets"].cuda()
     for label0, Ls in ((0, L), (1024, 2000)):
