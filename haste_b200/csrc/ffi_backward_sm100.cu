@@ -17,7 +17,7 @@
 // is equal modulo 8 share the misalignment, so each warp takes one such class and the shift is warp-uniform.
 // Columns at and beyond L are zeroed in the same pass (their neighbours in memory belong to the next row).
 //
-// Warp roles (832 threads): warps 0, 2, 24, 25 gather X tiles with TMA tile::gather4 (warp 0 also loads the W tile
+// Warp roles (24 or 25 warps): warps 0, 2 (and 24) gather X tiles with TMA tile::gather4 (warp 0 also loads the W tile
 // through a tensor map), warp 1 issues backward-features, warp 3 backward-weights, warps 4-11 drain dXg (TMEM ->
 // registers -> coalesced red.global.add.f32), warps 12-15 turn the dW accumulator into bf16 rows of dw / dbias at
 // the end of each group, warps 16-23 are the Y warps.  All waits are bounded (see mbar_wait).
@@ -35,8 +35,10 @@ struct Cfg {
   static constexpr int G = G_, F = F_, BT = 128;
   static_assert((G == 128 && F == 64) || (G == 64 && F == 128), "shapes with a tcgen05 backward");
   static constexpr int FR = F + 16;                   // X block rows: F gathered rows, one row of ones, 15 zero rows
-  static constexpr int NXS = 4;                       // X ring stages
-  static constexpr int NYS = (G == 128) ? 3 : 2;      // dY ring stages
+  // Shared memory goes to the dY ring first: dY streams from HBM (several microseconds from request to arrival under
+  // load, and a tile that has arrived still has to be shifted), the X rows come out of L2.
+  static constexpr int NXS = (F == 64) ? 2 : 3;       // X ring stages
+  static constexpr int NYS = 4;                       // dY ring stages
   static constexpr int NDX = 2;                       // dXg accumulator stages
   static constexpr int NDW = (F == 64) ? 2 : 1;       // dW accumulator stages
   static constexpr int XBLK = FR * 128, XSTAGE = 2 * XBLK;
@@ -63,7 +65,7 @@ struct Cfg {
   static constexpr int EBS = F / 2;                   // slots per scatter warp
   static constexpr int N_EC = 4;                      // dW writer warps: one per TMEM lane quarter
   static constexpr int N_Y = 8;                       // Y warps: one per row class (row index modulo 8)
-  static constexpr int NPW = 4;                       // X producer warps: 0, 2 and two after the Y warps
+  static constexpr int NPW = NXS;                     // X producer warps: 0, 2 and (at three stages) one after the Y warps
   static_assert(NPW <= NXS, "a producer must not run more than one phase ahead on any stage barrier");
   static constexpr int W_EB = 4, W_EC = W_EB + N_EB, W_Y = W_EC + N_EC, W_XP = W_Y + N_Y;
   static constexpr int NTHREADS = (W_XP + NPW - 2) * 32;
@@ -205,7 +207,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
     // ================================================================ Y warps: dY slice -> aligned, swizzled Y tile
     // Warp k owns the rows r = k, k + 8, ... of every tile.  Copies run LAG tiles ahead of the shifting.
     const int k = warp - C::W_Y;
-    constexpr int LAG = NYS - 1;
+    constexpr int LAG = NYS - 1;                       // tiles between the start of a copy and its hand-over
     constexpr int PER_ROW = NCH + 1;
     constexpr int N_CP = 16 * PER_ROW;                 // copies per warp and tile
     const uintptr_t dy_base = reinterpret_cast<uintptr_t>(a.dy);
@@ -214,37 +216,12 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
     const int rr = lane >> 3, c = lane & 7;            // shifting: lane = (row within a set of four, chunk within a 64-label block)
     int gi_i = 0, t_i = 0;                             // issue position
     int gi_p = 0, t_p = 0;                             // shift position
+    // Order inside an iteration: first hand over the tile whose copies have landed (shift, then arrive), only then
+    // wait for a free stage and start the next copies — a tile that is ready never waits for the tensor core to
+    // finish an older one.
     for (int it = 0; it < n_items + LAG; ++it) {
-      if (it < n_items) {
-        const int ys = it % NYS;
-        const bool ok = mbar_wait(bar(C::B_YEMPTY + ys), ((it / NYS) & 1) ^ 1, abort_flag, a.err, 33, WL, 100);
-        __syncwarp();
-        if (ok && !*abort_flag) {
-          const int64_t l0 = static_cast<int64_t>(group_of(gi_i)) * G;
-          const int64_t b0 = static_cast<int64_t>(t_i) * BT;
-          const uint32_t yb = sbase + C::OFF_Y + ys * YSTAGE, yside = sbase + C::OFF_YSIDE + ys * C::YSIDE;
-#pragma unroll
-          for (int j = 0; j < (N_CP + 31) / 32; ++j) {
-            const int idx = lane + 32 * j;
-            if (idx < N_CP) {
-              const int ri = idx / PER_ROW, ch = idx % PER_ROW;
-              const int r = k + 8 * ri;
-              const int64_t b = b0 + r;
-              const uintptr_t row_addr = dy_base + 2ull * static_cast<uint64_t>(b * a.ldy + l0);
-              const uintptr_t src = (row_addr & ~static_cast<uintptr_t>(15)) + 16u * ch;
-              // a chunk is read when it holds at least one byte of the tensor (it lies in the same 16-byte granule as
-              // that byte); everything else is zero-filled
-              const bool valid = b < a.B && src + 16 > dy_base && src < dy_end && (ch < NCH || (row_addr & 15) != 0);
-              const uint32_t dst = ch < NCH ? yb + (ch >> 3) * YBLK + r * 128 + (((ch & 7) ^ (r & 7)) << 4) : yside + r * 16;
-              cp_async16(dst, valid ? reinterpret_cast<const void*>(src) : reinterpret_cast<const void*>(dy_base & ~static_cast<uintptr_t>(15)), valid);
-            }
-          }
-        }
-        if (++t_i == T) { t_i = 0; ++gi_i; }
-      }
-      cp_async_commit();
       if (it >= LAG) {
-        cp_async_wait<LAG>();                          // this lane's copies of tile it - LAG have landed
+        cp_async_wait<LAG - 1>();                      // this lane's copies of tile it - LAG have landed (groups 0 .. it-1 are committed)
         __syncwarp();                                  // ... and so have the other lanes'
         const int jt = it - LAG, ys = jt % NYS;
         const int64_t l0 = static_cast<int64_t>(group_of(gi_p)) * G;
@@ -256,6 +233,8 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
           const uint32_t wo = sh >> 2, hb = (sh & 2u) << 3;     // whole words, then 0 or 16 bits
           uint8_t* yb = sm + C::OFF_Y + ys * YSTAGE;
           const uint8_t* yside = sm + C::OFF_YSIDE + ys * C::YSIDE;
+          // (Unrolling this over the four row sets, so that their shared-memory latencies overlap, made the whole
+          // kernel slower in measurement — aligned inputs included — and is therefore not done.)
 #pragma unroll 1
           for (int set = 0; set < 4; ++set) {
             const int r = k + 8 * (4 * set + rr);
@@ -295,6 +274,34 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
         if (lane == 0) mbar_arrive(bar(C::B_YFULL + ys));
         if (++t_p == T) { t_p = 0; ++gi_p; }
       }
+      if (it < n_items) {
+        const int ys = it % NYS;
+        const bool ok = mbar_wait(bar(C::B_YEMPTY + ys), ((it / NYS) & 1) ^ 1, abort_flag, a.err, 33, WL, 100);
+        __syncwarp();
+        if (ok && !*abort_flag) {
+          const int64_t l0 = static_cast<int64_t>(group_of(gi_i)) * G;
+          const int64_t b0 = static_cast<int64_t>(t_i) * BT;
+          const uint32_t yb = sbase + C::OFF_Y + ys * YSTAGE, yside = sbase + C::OFF_YSIDE + ys * C::YSIDE;
+#pragma unroll
+          for (int j = 0; j < (N_CP + 31) / 32; ++j) {
+            const int idx = lane + 32 * j;
+            if (idx < N_CP) {
+              const int ri = idx / PER_ROW, ch = idx % PER_ROW;
+              const int r = k + 8 * ri;
+              const int64_t b = b0 + r;
+              const uintptr_t row_addr = dy_base + 2ull * static_cast<uint64_t>(b * a.ldy + l0);
+              const uintptr_t src = (row_addr & ~static_cast<uintptr_t>(15)) + 16u * ch;
+              // a chunk is read when it holds at least one byte of the tensor (it lies in the same 16-byte granule as
+              // that byte); everything else is zero-filled
+              const bool valid = b < a.B && src + 16 > dy_base && src < dy_end && (ch < NCH || (row_addr & 15) != 0);
+              const uint32_t dst = ch < NCH ? yb + (ch >> 3) * YBLK + r * 128 + (((ch & 7) ^ (r & 7)) << 4) : yside + r * 16;
+              cp_async16(dst, valid ? reinterpret_cast<const void*>(src) : reinterpret_cast<const void*>(dy_base & ~static_cast<uintptr_t>(15)), valid);
+            }
+          }
+        }
+        if (++t_i == T) { t_i = 0; ++gi_i; }
+      }
+      cp_async_commit();
     }
     cp_async_wait<0>();
   } else if (warp == 1 || warp == 3) {
