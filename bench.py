@@ -140,6 +140,14 @@ def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, c
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    if world > 1:
+        # the first collectives of a communicator set up channels and buffers: keep that out of every timed step (the
+        # layer reduces dX on a communicator of its own, its flush() on the default one)
+        warm = torch.zeros_like(dev_batches[0][0], dtype=torch.float32)
+        for _ in range(25):
+            dist.all_reduce(warm, group=layer.comm_pg)
+            dist.all_reduce(warm)
+        barrier()
     for i in range(warmup):
         flush.zero_()
         one(i)
@@ -246,13 +254,6 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
-
-    if world > 1:
-        # the first collectives of a communicator set up channels and buffers: keep that out of every timed step
-        warm = torch.zeros(D, B, dtype=torch.float32, device=device)
-        for _ in range(25):
-            dist.all_reduce(warm)
-        barrier()
 
     # ---------------- device-resident steps: per-step CUDA events, L2 flushed in between
     step_ms, t_wall, clocks = _time_steps(layer, dev_batches, args.steps, args.warmup, world, device, flush, dist, clocks_index=local)
