@@ -65,14 +65,43 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs: NVML from a thread of this process (a first
+    sample at once, then one every 10 ms, so that a region of a few milliseconds is still covered); nvidia-smi as a
+    child process when the NVML module is missing.  Read-only queries."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.proc, self.path = index, None, None
+        self.rows, self.thread, self.stop, self.max_mhz = [], None, False, None
+
+    def _nvml_loop(self, nv, h):
+        while True:
+            try:
+                self.rows.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+            except Exception:
+                pass
+            if self.stop:
+                return
+            time.sleep(0.01)
 
     def __enter__(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                h = nv.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.nv = nv
+            import threading
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
@@ -83,6 +112,9 @@ class ClockSampler:
         return self
 
     def __exit__(self, *a):
+        if self.thread is not None:
+            self.stop = True
+            self.thread.join(timeout=2)
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
@@ -94,6 +126,16 @@ class ClockSampler:
     def summary(self):
         out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
         try:
+            if self.thread is not None:
+                nv = self.nv
+                bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                        "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+                out["sm_mhz"] = float(statistics.median(r[0] for r in self.rows))
+                out["sm_max_mhz"] = self.max_mhz
+                out["reasons"] = [n for n, b in bits.items() if any(r[1] & b for r in self.rows)]
+                out["samples"] = len(self.rows)
+                out["source"] = "nvml"
+                return out
             rows = [l.strip().split(",") for l in open(self.path) if l.strip()]
             sm = [float(r[0]) for r in rows]
             out["sm_mhz"] = statistics.median(sm)
@@ -101,6 +143,7 @@ class ClockSampler:
             names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
             out["reasons"] = [n for i, n in enumerate(names) if any("Active" in r[2 + i] and "Not" not in r[2 + i] for r in rows)]
             out["samples"] = len(rows)
+            out["source"] = "nvidia-smi"
         except Exception:
             pass
         return out
@@ -335,7 +378,8 @@ def run_ours(args):
         launches_per_step = 2 if world == 1 else 2            # preparation launch + fused kernel (the collective is NCCL's)
         line = {
             "metric": METRIC, "value": B / (ms_per_step * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "ms_per_step_mean": ms_mean, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "ms_per_step_mean": ms_mean, "ms_per_step_max": max(step_ms), "slowest_step": step_ms.index(max(step_ms)),
+            "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": _workload_string(args.workload, c) + " rng=packed",
                        "parallelism": (f"labels sharded over {world} rank(s), features replicated, dX all-reduce"
