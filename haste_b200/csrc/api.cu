@@ -102,6 +102,8 @@ int haste_ffi_backward_features(const void* w, const int32_t* loc, const void* d
     cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
   }
+  if (backward_sm100_supported(nullptr, w, dy, nullptr, B, D, F, L, G))
+    return launch_backward_sm100(nullptr, w, loc, dy, dxt, nullptr, nullptr, nullptr, B, D, F, L, G, ldy, st);
   return launch_bwd_features(w, loc, dy, dxt, B, D, F, L, G, ldy, st);
 }
 
@@ -112,6 +114,8 @@ int haste_ffi_backward_weights(const void* xt, const int32_t* loc, const void* d
   REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(dw, who);
   if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
   if (ldy < L) return fail(HASTE_ERR_BAD_ARG, "%s: ldy=%lld < L=%lld", who, (long long)ldy, (long long)L);
+  if (backward_sm100_supported(xt, nullptr, dy, dw, B, D, F, L, G))
+    return launch_backward_sm100(xt, nullptr, loc, dy, nullptr, dw, dbias, nullptr, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
   return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
 }
 
@@ -127,7 +131,7 @@ int haste_ffi_backward(const void* xt, const void* w, const int32_t* loc, const 
     cudaError_t e = cudaMemsetAsync(dxt, 0, sizeof(float) * D * B, st);
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
   }
-  if (backward_sm100_supported(xt, w, dy, dw, B, D, F, L, G)) return launch_backward_sm100(xt, w, loc, dy, dxt, dw, dbias, B, D, F, L, G, ldy, st);
+  if (backward_sm100_supported(xt, w, dy, dw, B, D, F, L, G)) return launch_backward_sm100(xt, w, loc, dy, dxt, dw, dbias, nullptr, B, D, F, L, G, ldy, st);
   if (int rc = launch_bwd_features(w, loc, dy, dxt, B, D, F, L, G, ldy, st)) return rc;
   return launch_bwd_weights(xt, loc, dy, dw, dbias, nullptr, B, D, F, L, G, ldy, st);
 }
@@ -152,6 +156,8 @@ int haste_ffi_bww_sr_sgd(const void* xt, const int32_t* loc, const void* dy, voi
   u.w = static_cast<__nv_bfloat16*>(w); u.bias = static_cast<__nv_bfloat16*>(bias);
   u.mom_w = (mu != 0.f) ? mom_w : nullptr; u.mom_b = (mu != 0.f) ? mom_b : nullptr;
   u.lr = lr; u.wd = wd; u.mu = mu; u.seed = seed; u.step = step; u.flags = flags; u.label0 = label0;
+  if (backward_sm100_supported(xt, nullptr, dy, w, B, D, F, L, G))
+    return launch_backward_sm100(xt, nullptr, loc, dy, nullptr, nullptr, nullptr, &u, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
   return launch_bwd_weights(xt, loc, dy, nullptr, nullptr, &u, B, D, F, L, G, ldy, static_cast<cudaStream_t>(stream));
 }
 

@@ -91,9 +91,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int G_, int F_>
+// DX / DW: which gradients this instantiation produces (the roles of the other one are compiled out: its issuer, its
+// operand loads, its epilogue warps).  UPD (with DW): the dW writer warps apply SGD + weight decay (+ momentum) +
+// stochastic rounding to the weights and bias in global memory instead of storing the gradient.
+template <int G_, int F_, bool DX, bool DW, bool UPD>
 __global__ void __launch_bounds__(Cfg<G_, F_>::NTHREADS, 1)
-ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w) {
+ffi_backward_sm100_kernel(BwdArgs a, UpdateArgs u, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w) {
+  static_assert(DX || DW, "nothing to compute");
+  static_assert(!UPD || DW, "the update consumes the weight gradient");
   using C = Cfg<G_, F_>;
   constexpr int G = C::G, F = C::F, BT = C::BT, FR = C::FR, NXS = C::NXS, NYS = C::NYS, NDX = C::NDX, NDW = C::NDW;
   constexpr int XBLK = C::XBLK, XSTAGE = C::XSTAGE, WBLK = C::WBLK, WSTAGE = C::WSTAGE, YBLK = C::YBLK, YSTAGE = C::YSTAGE, NCH = C::NCH;
@@ -110,7 +115,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
 
   if (tid == 0) {
     for (int i = 0; i < NXS; ++i) { mbar_init(bar(C::B_XFULL + i), 1); mbar_init(bar(C::B_XEMPTY + i), 1); }
-    for (int i = 0; i < NYS; ++i) { mbar_init(bar(C::B_YFULL + i), C::N_Y); mbar_init(bar(C::B_YEMPTY + i), 2); }   // both issuers commit
+    for (int i = 0; i < NYS; ++i) { mbar_init(bar(C::B_YFULL + i), C::N_Y); mbar_init(bar(C::B_YEMPTY + i), (DX ? 1 : 0) + (DW ? 1 : 0)); }   // every issuer commits
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::B_WFULL + i), 1);  mbar_init(bar(C::B_WEMPTY + i), 1);
       mbar_init(bar(C::B_LEMPTY + i), C::N_EB);      // the scatter warps are done with the group's index row
@@ -154,7 +159,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       int locv[F / 32];
 #pragma unroll
       for (int j = 0; j < F / 32; ++j) locv[j] = min(max(__ldg(lrow + lane + 32 * j), 0), a.D - 1);   // clamped: never addresses outside xt / dxt
-      if (prod_id == 0) {
+      if (DX && prod_id == 0) {
         bool ok = mbar_wait(bar(C::B_WEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WL, 100);
         ok = mbar_wait(bar(C::B_LEMPTY + ws), ((gi >> 1) & 1) ^ 1, abort_flag, a.err, 31, WL, 100) && ok;
         __syncwarp();
@@ -180,7 +185,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       for (int j = 0; j < F / 32; ++j) locr[lane + 32 * j] = locv[j];
       __syncwarp();
       const int4* lr4 = reinterpret_cast<const int4*>(locr);
-      for (int t = 0; t < T; ++t, ++it) {
+      for (int t = 0; DW && t < T; ++t, ++it) {          // X is an operand of backward-weights only
         if (it % C::NPW != prod_id) continue;
         const int xs = it % NXS;
         const bool okx = mbar_wait(bar(C::B_XEMPTY + xs), ((it / NXS) & 1) ^ 1, abort_flag, a.err, 32, WL, 100);
@@ -312,7 +317,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
     const uint64_t D_WM = make_sdesc(sbase + C::OFF_W, WBLK, 1024);    // W tile as MN-major B   (backward-features)
     const uint64_t D_YA = make_sdesc(sbase + C::OFF_Y, 16, 1024);      // Y tile as K-major  A   (backward-features)
     const uint64_t D_YM = make_sdesc(sbase + C::OFF_Y, YBLK, 1024);    // Y tile as MN-major A   (backward-weights)
-    if (warp == 1) {
+    if (warp == 1 && DX) {
       const uint32_t wm_lo = static_cast<uint32_t>(D_WM), wm_hi = static_cast<uint32_t>(D_WM >> 32);
       const uint32_t ya_lo = static_cast<uint32_t>(D_YA), ya_hi = static_cast<uint32_t>(D_YA >> 32);
       const uint32_t id_bwx = ID_BWX;
@@ -344,7 +349,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       if (elect_one()) tc_commit(bar(C::B_FIN));
       __syncwarp();
       mbar_wait_final(bar(C::B_FIN), 0, WL);
-    } else {
+    } else if (warp == 3 && DW) {
       const uint32_t xb_lo = static_cast<uint32_t>(D_XB), xb_hi = static_cast<uint32_t>(D_XB >> 32);
       const uint32_t ym_lo = static_cast<uint32_t>(D_YM), ym_hi = static_cast<uint32_t>(D_YM >> 32);
       const uint32_t id_bww = ID_BWW;
@@ -377,7 +382,7 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       __syncwarp();
       mbar_wait_final(bar(C::B_FIN + 1), 0, WL);
     }
-  } else if (warp >= C::W_EB && warp < C::W_EC) {
+  } else if (DX && warp >= C::W_EB && warp < C::W_EC) {
     // ================================================================ scatter: dXg -> dxt
     const int q = warp & 3, kc = (warp - C::W_EB) >> 2;
     const int row = q * 32 + lane;               // TMEM lane == batch row inside the tile
@@ -420,12 +425,15 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::B_LEMPTY + ws));
     }
-  } else if (warp >= C::W_EC && warp < C::W_Y) {
+  } else if (DW && warp >= C::W_EC && warp < C::W_Y) {
     // ================================================================ dW / dbias rows out of the accumulator
-    // G = 128: TMEM lane == label row.  G = 64: an M = 64 accumulator occupies lanes 0-15 of each lane quarter, so
-    // only the lower half of the warp holds rows (the loads are warp-wide all the same).
+    // G = 128: TMEM lane == label row, every lane takes its row's 32 columns of each piece.  G = 64: an M = 64
+    // accumulator occupies lanes 0-15 of each lane quarter, so lane l and lane l + 16 share label row l: the upper 16
+    // columns of every 32-column piece go to lane l + 16 by shuffle and the whole warp works.
+    constexpr bool SPLIT = C::ROWS_PER_Q == 16;
+    constexpr int NCL = SPLIT ? 2 : 4;              // 8-slot chunks per lane and piece
     const int q = warp & 3;
-    const bool has_row = lane < C::ROWS_PER_Q;
+    const int half = SPLIT ? (lane >> 4) : 0;
     const int row = q * C::ROWS_PER_Q + (lane & (C::ROWS_PER_Q - 1));
     for (int gi = 0; gi < n_my_groups; ++gi) {
       const int g = group_of(gi);
@@ -435,21 +443,76 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       mbar_wait(bar(C::B_DWFULL + dws), (gi / NDW) & 1, abort_flag, a.err, 42, WL);
       tc_fence_after();
       const uint32_t ta = tmem + (static_cast<uint32_t>(q * 32) << 16) + C::TM_DW + dws * FR;
-      const bool do_row = has_row && row < rows_real && !*abort_flag;
-      uint4* out = reinterpret_cast<uint4*>(a.dw + (l0 + row) * F);
+      const bool do_row = row < rows_real && !*abort_flag;
+      const int64_t l = l0 + row, gl = u.label0 + l;
+      const bool fast = UPD && u.mom_w == nullptr && (u.flags & HASTE_F_SR) && (u.flags & HASTE_F_CONTRACT);
 #pragma unroll
       for (int pc = 0; pc < F / 32; ++pc) {
         uint32_t r0[32];
         __syncwarp();
         tmem_ld32(ta + pc * 32, r0);
         tmem_ld_wait();
+        if (SPLIT) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const uint32_t up = __shfl_sync(0xffffffffu, r0[16 + x], lane & 15);
+            if (half) r0[x] = up;
+          }
+        }
         if (do_row) {
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4)
-            out[pc * 4 + c4] = make_uint4(pack2(__uint_as_float(r0[8 * c4]), __uint_as_float(r0[8 * c4 + 1])),
-                                          pack2(__uint_as_float(r0[8 * c4 + 2]), __uint_as_float(r0[8 * c4 + 3])),
-                                          pack2(__uint_as_float(r0[8 * c4 + 4]), __uint_as_float(r0[8 * c4 + 5])),
-                                          pack2(__uint_as_float(r0[8 * c4 + 6]), __uint_as_float(r0[8 * c4 + 7])));
+          for (int c4 = 0; c4 < NCL; ++c4) {
+            const int s0 = pc * 32 + half * 16 + c4 * 8;        // first of this chunk's 8 slots
+            uint4* out = reinterpret_cast<uint4*>((UPD ? u.w : a.dw) + l * F + s0);
+            // the gradient as the unfused kernel would store it: rounded to bf16
+            const uint4 g8 = make_uint4(pack2(__uint_as_float(r0[8 * c4]), __uint_as_float(r0[8 * c4 + 1])),
+                                        pack2(__uint_as_float(r0[8 * c4 + 2]), __uint_as_float(r0[8 * c4 + 3])),
+                                        pack2(__uint_as_float(r0[8 * c4 + 4]), __uint_as_float(r0[8 * c4 + 5])),
+                                        pack2(__uint_as_float(r0[8 * c4 + 6]), __uint_as_float(r0[8 * c4 + 7])));
+            if (!UPD) {
+              *out = g8;
+            } else {
+              const uint4 w8 = *out;
+              const uint32_t gw[4] = {g8.x, g8.y, g8.z, g8.w}, ww[4] = {w8.x, w8.y, w8.z, w8.w};
+              uint32_t rnd[4] = {0u, 0u, 0u, 0u};               // 8 x 16 random bits, two per word
+              if (u.flags & HASTE_F_SR) {
+                if (u.flags & HASTE_F_RNG_PACKED) {
+                  const uint4 rp = rand_packed8(u.seed, u.step, gl, s0 >> 3);
+                  rnd[0] = rp.x; rnd[1] = rp.y; rnd[2] = rp.z; rnd[3] = rp.w;
+                } else {
+#pragma unroll
+                  for (int x = 0; x < 4; ++x)
+                    rnd[x] = rand16_reference(u.seed, gl * F + s0 + 2 * x) | (rand16_reference(u.seed, gl * F + s0 + 2 * x + 1) << 16);
+                }
+              }
+              uint32_t ob[4];
+              if (fast) {
+                // no momentum, stochastic rounding, fused multiply-add: w' = fma(-lr, fma(wd, w, g), w), then add 16
+                // random bits and keep the high half
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  const float g0 = __uint_as_float(gw[x] << 16), g1 = __uint_as_float(gw[x] & 0xFFFF0000u);
+                  const float w0 = __uint_as_float(ww[x] << 16), w1 = __uint_as_float(ww[x] & 0xFFFF0000u);
+                  const float n0 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w0, g0), w0), n1 = __fmaf_rn(-u.lr, __fmaf_rn(u.wd, w1, g1), w1);
+                  ob[x] = __byte_perm(__float_as_uint(n0) + (rnd[x] & 0xFFFFu), __float_as_uint(n1) + (rnd[x] >> 16), 0x7632);
+                }
+              } else {
+                float* mrow = u.mom_w != nullptr ? u.mom_w + l * F + s0 : nullptr;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  float m0 = 0.f, m1 = 0.f;
+                  if (mrow) { m0 = mrow[2 * x]; m1 = mrow[2 * x + 1]; }
+                  const uint32_t o0 = sgd_update_bits(static_cast<uint16_t>(ww[x] & 0xFFFFu), __uint_as_float(gw[x] << 16), mrow ? &m0 : nullptr,
+                                                      u.lr, u.wd, u.mu, u.flags, rnd[x] & 0xFFFFu);
+                  const uint32_t o1 = sgd_update_bits(static_cast<uint16_t>(ww[x] >> 16), __uint_as_float(gw[x] & 0xFFFF0000u),
+                                                      mrow ? &m1 : nullptr, u.lr, u.wd, u.mu, u.flags, rnd[x] >> 16);
+                  ob[x] = o0 | (o1 << 16);
+                  if (mrow) { mrow[2 * x] = m0; mrow[2 * x + 1] = m1; }
+                }
+              }
+              *out = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+            }
+          }
         }
       }
       uint32_t rb[8];
@@ -459,7 +522,19 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::B_DWEMPTY + dws));
-      if (do_row && a.dbias != nullptr) a.dbias[l0 + row] = __float2bfloat16_rn(__uint_as_float(rb[0]));
+      if (half == 0) {
+        if (!UPD) {
+          if (do_row && a.dbias != nullptr) a.dbias[l] = __float2bfloat16_rn(__uint_as_float(rb[0]));
+        } else if (do_row && u.bias != nullptr) {
+          const float gb = round_to_bf16_f(__uint_as_float(rb[0]));
+          uint32_t r16 = 0;
+          if (u.flags & HASTE_F_SR) r16 = rand16(u.flags, u.seed ^ ((u.flags & HASTE_F_RNG_PACKED) ? 0x62696173ull : 0ull), u.step, gl, 0, 1);
+          float m = u.mom_b != nullptr ? u.mom_b[l] : 0.f;
+          u.bias[l] = __ushort_as_bfloat16(sgd_update_bits(__bfloat16_as_ushort(u.bias[l]), gb, u.mom_b != nullptr ? &m : nullptr, u.lr, u.wd,
+                                                           u.mu, u.flags, r16));
+          if (u.mom_b != nullptr) u.mom_b[l] = m;
+        }
+      }
     }
   }
 
@@ -469,33 +544,51 @@ ffi_backward_sm100_kernel(BwdArgs a, const __grid_constant__ CUtensorMap tm_x, c
 }
 
 template <int G_, int F_>
-static int launch_shape(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
-                        int64_t D, int64_t L, int64_t ldy, cudaStream_t st) {
+static int launch_shape(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias,
+                        const UpdateArgs* upd, int64_t B, int64_t D, int64_t L, int64_t ldy, cudaStream_t st) {
   using C = Cfg<G_, F_>;
   if (int rc = report_pending_status("tcgen05 backward")) return rc;
   int* err_dev = nullptr;
   if (int rc = device_status_word(&err_dev)) return rc;
+  const bool want_dx = dxt != nullptr, want_dw = dw != nullptr || upd != nullptr;
   BwdArgs a;
   a.loc = loc; a.dy = static_cast<const __nv_bfloat16*>(dy); a.dxt = dxt; a.dw = static_cast<__nv_bfloat16*>(dw);
   a.dbias = static_cast<__nv_bfloat16*>(dbias); a.err = err_dev;
   a.B = B; a.L = L; a.ldy = ldy; a.D = static_cast<int>(D); a.NG = static_cast<int>((L + C::G - 1) / C::G);
   a.wait_limit = wait_limit_cycles();
+  UpdateArgs u{};
+  if (upd) u = *upd;
+  // a gradient that is not asked for needs neither its operand nor that operand's tensor map (the kernel never uses it)
   CUtensorMap tm_x, tm_w;
-  if (int rc = make_tmap_bf16_2d(&tm_x, xt, static_cast<uint64_t>(B), static_cast<uint64_t>(D), static_cast<uint64_t>(B) * 2, 64, 1)) return rc;
-  if (int rc = make_tmap_bf16_2d(&tm_w, w, static_cast<uint64_t>(C::F), static_cast<uint64_t>(L), static_cast<uint64_t>(C::F) * 2, 64, C::G)) return rc;
+  const void* w_map = want_dx ? w : xt;
+  const void* x_map = want_dw ? xt : w;
+  if (want_dw) { if (int rc = make_tmap_bf16_2d(&tm_x, x_map, static_cast<uint64_t>(B), static_cast<uint64_t>(D), static_cast<uint64_t>(B) * 2, 64, 1)) return rc; }
+  if (want_dx) { if (int rc = make_tmap_bf16_2d(&tm_w, w_map, static_cast<uint64_t>(C::F), static_cast<uint64_t>(L), static_cast<uint64_t>(C::F) * 2, 64, C::G)) return rc; }
+  if (!want_dw) tm_x = tm_w;
+  if (!want_dx) tm_w = tm_x;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = a.NG < sms ? a.NG : sms;
-  auto k = ffi_backward_sm100_kernel<G_, F_>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-  if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, tm_x, tm_w);
+#define HASTE_B100_LAUNCH(DXF, DWF, UPDF)                                                                     \
+  {                                                                                                          \
+    auto k = ffi_backward_sm100_kernel<G_, F_, DXF, DWF, UPDF>;                                              \
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);     \
+    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));  \
+    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_x, tm_w);                                           \
+  }
+  if (want_dx && want_dw && !upd) HASTE_B100_LAUNCH(true, true, false)
+  else if (want_dx && !want_dw) HASTE_B100_LAUNCH(true, false, false)
+  else if (!want_dx && want_dw && !upd) HASTE_B100_LAUNCH(false, true, false)
+  else if (!want_dx && upd) HASTE_B100_LAUNCH(false, true, true)
+  else return fail(HASTE_ERR_UNSUPPORTED, "tcgen05 backward: this combination of outputs has no instantiation");
+#undef HASTE_B100_LAUNCH
   return check_launch("ffi_backward_sm100_kernel");
 }
 
 }  // namespace b100
 
+// xt / w / dw may be NULL when the gradient that needs them is not asked for.
 bool backward_sm100_supported(const void* xt, const void* w, const void* dy, const void* dw, int64_t B, int64_t D, int64_t F, int64_t L,
                               int64_t G) {
   // tensor maps need 16-byte aligned bases and row strides; dxt row offsets and tile coordinates are 32-bit; dy only
@@ -504,10 +597,12 @@ bool backward_sm100_supported(const void* xt, const void* w, const void* dy, con
          (reinterpret_cast<uintptr_t>(dy) & 1u) == 0 && D * B < (int64_t(1) << 32) && L < (int64_t(1) << 31) && B < (int64_t(1) << 31);
 }
 
-int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
-                          int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st) {
-  if (G == 128 && F == 64) return b100::launch_shape<128, 64>(xt, w, loc, dy, dxt, dw, dbias, B, D, L, ldy, st);
-  if (G == 64 && F == 128) return b100::launch_shape<64, 128>(xt, w, loc, dy, dxt, dw, dbias, B, D, L, ldy, st);
+// dxt == NULL: weight gradient only; dw == NULL and upd == NULL: feature gradient only; upd != NULL (with dxt == NULL):
+// backward-weights fused with the update of upd->w / upd->bias.
+int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias,
+                          const UpdateArgs* upd, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st) {
+  if (G == 128 && F == 64) return b100::launch_shape<128, 64>(xt, w, loc, dy, dxt, dw, dbias, upd, B, D, L, ldy, st);
+  if (G == 64 && F == 128) return b100::launch_shape<64, 128>(xt, w, loc, dy, dxt, dw, dbias, upd, B, D, L, ldy, st);
   return fail(HASTE_ERR_UNSUPPORTED, "tcgen05 backward: no kernel for group size %lld, fan-in %lld", (long long)G, (long long)F);
 }
 

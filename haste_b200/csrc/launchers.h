@@ -63,8 +63,8 @@ int launch_step_prepare(const void* x, void* xt, float* dxt, float* loss, const 
                         int64_t G, int32_t* ptr, uint32_t* ent, int64_t B, int64_t D, cudaStream_t st);
 bool backward_sm100_supported(const void* xt, const void* w, const void* dy, const void* dw, int64_t B, int64_t D, int64_t F, int64_t L,
                               int64_t G);
-int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias, int64_t B,
-                          int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st);
+int launch_backward_sm100(const void* xt, const void* w, const int32_t* loc, const void* dy, float* dxt, void* dw, void* dbias,
+                          const UpdateArgs* upd, int64_t B, int64_t D, int64_t F, int64_t L, int64_t G, int64_t ldy, cudaStream_t st);
 int launch_pad_rows(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols, cudaStream_t st);
 int launch_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int k, float* vals, int32_t* idx, cudaStream_t st);
 int launch_check_loc(const int32_t* loc, int64_t n, int64_t D, cudaStream_t st);
