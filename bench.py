@@ -73,7 +73,20 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc, self.path = index, None, None
-        self.rows, self.thread, self.stop, self.max_mhz = [], None, False, None
+        self.rows, self.thread, self.stop, self.max_mhz, self.nv, self.handle = [], None, False, None, None, None
+        try:                                   # library start-up costs milliseconds: here, not inside a timed region
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                h = nv.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+            self.nv, self.handle = nv, h
+        except Exception:
+            self.nv = None
 
     def _nvml_loop(self, nv, h):
         while True:
@@ -86,22 +99,11 @@ class ClockSampler:
             time.sleep(0.01)
 
     def __enter__(self):
-        try:
-            import pynvml as nv
-            nv.nvmlInit()
-            try:
-                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
-                h = nv.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
-            except Exception:
-                h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-            self.nv = nv
+        if self.nv is not None:
             import threading
-            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(self.nv, self.handle), daemon=True)
             self.thread.start()
             return self
-        except Exception:
-            self.thread = None
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
@@ -183,6 +185,7 @@ def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, c
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    sampler = ClockSampler(clocks_index) if clocks_index is not None else None
     if world > 1:
         # the first collectives of a communicator set up channels and buffers: keep that out of every timed step (the
         # layer reduces dX on a communicator of its own, its flush() on the default one)
@@ -196,7 +199,6 @@ def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, c
         one(i)
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    sampler = ClockSampler(clocks_index) if clocks_index is not None else None
     if sampler:
         sampler.__enter__()
     t_wall0 = time.perf_counter()
@@ -299,7 +301,8 @@ def run_ours(args):
         torch.cuda.synchronize(device)
 
     # ---------------- device-resident steps: per-step CUDA events, L2 flushed in between
-    step_ms, t_wall, clocks = _time_steps(layer, dev_batches, args.steps, args.warmup, world, device, flush, dist, clocks_index=local)
+    step_ms, t_wall, clocks = _time_steps(layer, dev_batches, args.steps, args.warmup, world, device, flush, dist,
+                                          clocks_index=local if rank == 0 else None)    # rank 0's GPU is sampled
     ms_per_step = statistics.median(step_ms)
     ms_mean = statistics.mean(step_ms)
 
