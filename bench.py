@@ -197,10 +197,10 @@ def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, c
     for i in range(warmup):
         flush.zero_()
         one(i)
+    if sampler:
+        sampler.__enter__()          # the sampling thread starts while the warm-up drains, not inside the first timed step
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    if sampler:
-        sampler.__enter__()
     t_wall0 = time.perf_counter()
     for i in range(steps):
         flush.zero_()
