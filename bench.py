@@ -189,6 +189,7 @@ def _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist, c
     if world > 1:
         # the first collectives of a communicator set up channels and buffers: keep that out of every timed step (the
         # layer reduces dX on a communicator of its own, its flush() on the default one)
+        layer.setup_pipeline(dev_batches[0][0].shape[0])
         warm = torch.zeros_like(dev_batches[0][0], dtype=torch.float32)
         for _ in range(25):
             dist.all_reduce(warm, group=layer.comm_pg)

@@ -183,7 +183,7 @@ class ShardedFFILayer:
     """
 
     def __init__(self, full_locations, full_weights, full_bias, group_size, in_features, device, *, process_group=None,
-                 rank=None, world_size=None, group_cost=None, reserve_sms=16, **shard_kwargs):
+                 rank=None, world_size=None, group_cost=None, reserve_sms=None, **shard_kwargs):
         import torch.distributed as dist
         self.dist = dist
         self.pg = process_group
@@ -207,26 +207,11 @@ class ShardedFFILayer:
         on_gpu = torch.device(device).type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if (world_size > 1 and on_gpu) else None
         self.prep_stream = torch.cuda.Stream(device=device) if on_gpu else None
-        self.reserve_sms = int(reserve_sms)
-        # The pipelined step's all-reduce runs beside the persistent fused kernel, which holds every SM but
-        # ``reserve_sms``.  A collective that asks for more CTAs than that gets some of them only after the fused kernel's
-        # CTAs, or takes SMs from them (a fused-kernel CTA needs a whole SM's shared memory): either way the step becomes
-        # kernel + collective instead of their maximum.  So the dX all-reduce gets its own communicator, capped at
-        # ``reserve_sms`` CTAs that are launched singly, not as clusters of four (a cluster needs four free SMs of one GPC
-        # at the same moment).  Measured on four B200s at 670K labels: kernel alone on 132 CTAs 100 us, all-reduce of the
-        # 1.5 MB dX alone 45 us; together 122 us with the default communicator, 105 us with this one (and 120 us with 8
-        # reserved SMs and 8 CTAs: an 8-CTA all-reduce takes 82 us by itself).
-        self.comm_pg = process_group
-        if world_size > 1 and on_gpu and dist.is_initialized() and dist.get_backend(process_group) == "nccl":
-            try:
-                opts = dist.ProcessGroupNCCL.Options()
-                opts.config.max_ctas = max(1, self.reserve_sms)
-                opts.config.min_ctas = 1
-                opts.config.cga_cluster_size = 1
-                self.comm_pg = dist.new_group(ranks=dist.get_process_group_ranks(process_group if process_group is not None else dist.group.WORLD),
-                                              backend="nccl", pg_options=opts)
-            except (AttributeError, TypeError, RuntimeError):     # a torch without these options: the caller's group as it is
-                self.comm_pg = process_group
+        # SMs the pipelined step leaves to the side streams; None = chosen at the first pipelined step (_choose_reserve)
+        self.reserve_sms = None if reserve_sms is None else int(reserve_sms)
+        self.comm_pg = process_group          # replaced by a communicator of the layer's own at the first pipelined step
+        self._comm_ready = False
+        self._on_gpu = on_gpu
         self._slots = None          # pipelined path: three sets of per-batch buffers (being reduced / computed / prepared)
         self._cur = 0               # slot of the batch the next step_pipelined call computes on
         self._staged = False        # slot _cur already holds a prepared batch
@@ -240,6 +225,49 @@ class ShardedFFILayer:
         return dxt, loss
 
     # ------------------------------------------------------------------ pipelined path
+    def _choose_reserve(self, B):
+        """SMs left free for the collective and the preparation kernel.  The all-reduce of the 4*D*B bytes of dX gets
+        slower with fewer CTAs and with more ranks (four B200s, 1.5 MB: 45 us with NCCL's default, 55 us with 16 CTAs, 82
+        us with 8), the fused kernel gets slower with fewer SMs, and a kernel much longer than the collective loses more
+        from missing SMs than it can win from the overlap.  Measured at 670K labels (per-step time, 8 / 12 / 16 SMs
+        reserved): four ranks 88 / 85 / 87 us, eight ranks 90 / 70 / 60 us; at 2.8M labels on four ranks 630 / - / 654 us."""
+        sh = self.shard
+        est_kernel_ms = 6.0 * B * sh.L * sh.F / 500e12 * 1e3        # the fused kernel sustains about 500 TFLOP/s
+        if est_kernel_ms > 0.5 or self.world <= 2:
+            return 8
+        return 12 if self.world <= 4 else 16
+
+    def _make_comm(self):
+        """The pipelined step's all-reduce runs beside the persistent fused kernel, which holds every SM but
+        ``reserve_sms``.  A collective that asks for more CTAs than that gets some of them only after the fused kernel's
+        CTAs retire, or takes SMs from them (a fused-kernel CTA needs a whole SM's shared memory): either way the step
+        becomes kernel + collective instead of their maximum.  So the dX all-reduce gets its own communicator, capped at
+        ``reserve_sms`` CTAs that are launched singly, not as clusters of four (a cluster needs four free SMs of one GPC
+        at the same moment).  Measured on four B200s at 670K labels: kernel alone on 132 CTAs 100 us, all-reduce of the
+        1.5 MB dX alone 45 us; together 122 us with the default communicator, 105 us with this one.  Collective call:
+        every rank reaches its first pipelined step at the same point of its program."""
+        dist = self.dist
+        self._comm_ready = True
+        if not (self.world > 1 and self._on_gpu and dist.is_initialized() and dist.get_backend(self.pg) == "nccl"):
+            return
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = max(1, self.reserve_sms)
+            opts.config.min_ctas = 1
+            opts.config.cga_cluster_size = 1
+            self.comm_pg = dist.new_group(ranks=dist.get_process_group_ranks(self.pg if self.pg is not None else dist.group.WORLD),
+                                          backend="nccl", pg_options=opts)
+        except (AttributeError, TypeError, RuntimeError):     # a torch without these options: the caller's group as it is
+            self.comm_pg = self.pg
+
+    def setup_pipeline(self, B):
+        """Chooses ``reserve_sms`` (unless given) and creates the all-reduce communicator for batches of ``B`` rows; called
+        by the first ``step_pipelined`` when the caller has not done it (a collective call: same point on every rank)."""
+        if self.reserve_sms is None:
+            self.reserve_sms = self._choose_reserve(B)
+        if not self._comm_ready:
+            self._make_comm()
+
     def _make_slots(self, B, D, nnz, dev):
         sh = self.shard
         self._slots = [dict(xt=torch.empty(D, B, dtype=torch.bfloat16, device=dev), dxt=torch.empty(D, B, dtype=torch.float32, device=dev),
@@ -266,6 +294,7 @@ class ShardedFFILayer:
         if self._slots is None or self._slots[0]["xt"].shape != (D, B):
             self._make_slots(B, D, max(targets.shape[0], 1 if next_batch is None else next_batch[1].shape[0]), dev)
             if self.world > 1:      # leave SMs free for the collective and the preparation kernels of the other streams
+                self.setup_pipeline(B)
                 _lib.check(_lib.lib.haste_ffi_set_max_ctas(max(1, _sm_count(dev) - self.reserve_sms)), "set_max_ctas")
         s = self._cur
         nxt = (s + 1) % 3           # the previous step's slot is (s + 2) % 3: three distinct buffers are live per call
