@@ -724,6 +724,103 @@ def probe_rows(c, xt, dev, peaks, timeit):
     return rows
 
 
+def run_comm_probe(args):
+    """N > 1 (under torchrun): what the pipelined step's time is made of on the chosen workload.  Per-measurement CUDA
+    events after a barrier + synchronise, MAX over ranks of the median of 30: the fused kernel alone at several CTA
+    counts, the all-reduce of dX alone with the default communicator and with CTA-capped ones, the two side by side,
+    and the per-step time of the real pipelined loop against the number of reserved SMs.  One JSON line per figure."""
+    import torch.distributed as dist
+    from haste_b200 import _lib, ffi as hffi, synth
+    from haste_b200.fused import ShardedFFILayer
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if world < 2:
+        raise SystemExit("--comm-probe needs N > 1 ranks (launch under torch.distributed.run)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    c = synth.WORKLOADS[args.workload]
+    B, D, L, F, G = c["B"], c["D"], c["L"], c["F"], c["G"]
+    loc, W, bias = synth.make_layer(D, L, F, G, seed=42)
+    grad_scale = 1.0 / (B * L) if c["loss"] == "squared_hinge" else 1.0
+    batches = [synth.make_batch(B, D, L, c["avg_pos"], c["zipf"], c["x"], seed=1000 + i) for i in range(N_BATCHES)]
+    dev_batches = [(x.to(device), t.to(device)) for x, t in batches]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    cur, side = torch.cuda.current_stream(device), torch.cuda.Stream(device=device)
+    kw = dict(rank=rank, world_size=world, loss=c["loss"], lr=LR, weight_decay=WD, seed=SEED, rng="packed", grad_scale=grad_scale)
+
+    def emit(what, us):
+        if rank == 0:
+            print(json.dumps({"probe": what, "workload": args.workload, "n_gpus": world, "us": round(us, 1)}), flush=True)
+
+    def capped(n, cga=1):
+        o = dist.ProcessGroupNCCL.Options()
+        o.config.max_ctas, o.config.min_ctas, o.config.cga_cluster_size = n, 1, cga
+        return dist.new_group(backend="nccl", pg_options=o)
+
+    def timed(fn, n=30):
+        ts = []
+        for i in range(n + 5):
+            flush.zero_()
+            dist.barrier()
+            torch.cuda.synchronize(device)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(cur); fn(); b.record(cur)
+            torch.cuda.synchronize(device)
+            if i >= 5:
+                ts.append(a.elapsed_time(b))
+        v = torch.tensor([statistics.median(ts)], device=device)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v) * 1e3
+
+    layer = ShardedFFILayer(loc, W, bias, G, D, device, **kw)
+    sh = layer.shard
+    xt = hffi.transpose_bf16(dev_batches[0][0])
+    sh.bucket_targets(dev_batches[0][1])
+    dxt, buf = torch.zeros(D, B, device=device), torch.zeros(D, B, device=device)
+
+    def kern():
+        seed, stp = sh._keys()
+        hffi.train_step(sh.loc, xt, sh.w, sh.bias, None, None, sh.tgt_ptr, sh.tgt_ent, dxt, sh.loss_buf, sh.G, sh.label0, sh.loss_kind,
+                        sh.grad_scale, LR, WD, 0.0, seed, stp, hffi.make_flags(sr=True, contract=True, rng="packed", zero_dxt=False, loss=True))
+
+    def both(pg):
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        kern()
+        side.wait_event(ev)
+        with torch.cuda.stream(side):
+            dist.all_reduce(buf, group=pg)
+            done = torch.cuda.Event()
+            done.record(side)
+        cur.wait_event(done)
+
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    groups = {"default communicator": None, "at most 8 CTAs, launched singly": capped(8), "at most 16 CTAs, launched singly": capped(16),
+              "at most 32 CTAs, launched singly": capped(32)}
+    for free in (0, 8, 16):
+        _lib.check(_lib.lib.haste_ffi_set_max_ctas(sms - free if free else 0), "set_max_ctas")
+        emit(f"fused kernel alone, {free} SMs left free", timed(kern))
+    for name, pg in groups.items():
+        for _ in range(10):
+            dist.all_reduce(buf, group=pg)
+        emit(f"all-reduce of dX alone, {name}", timed(lambda: dist.all_reduce(buf, group=pg)))
+    for free in (8, 16):
+        _lib.check(_lib.lib.haste_ffi_set_max_ctas(sms - free), "set_max_ctas")
+        for name, pg in groups.items():
+            emit(f"kernel ({free} SMs left free) beside the all-reduce, {name}", timed(lambda: both(pg)))
+    del layer
+    for reserve, own in ((8, False), (8, True), (12, True), (16, True), (24, True)):
+        layer = ShardedFFILayer(loc, W, bias, G, D, device, reserve_sms=reserve, **kw)
+        if not own:
+            layer._comm_ready = True                  # keep the caller's (default) communicator for the dX all-reduce
+        ms, _, _ = _time_steps(layer, dev_batches, 60, 10, world, device, flush, dist)
+        emit(f"pipelined step, {reserve} SMs reserved, " + ("capped communicator" if own else "default communicator"), statistics.median(ms) * 1e3)
+        del layer
+        torch.cuda.empty_cache()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -734,9 +831,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the extra 2.8M-label measurement")
     ap.add_argument("--aux", action="store_true", help="time the unfused and streaming kernels instead of the train step")
+    ap.add_argument("--comm-probe", action="store_true", help="N > 1: kernel, all-reduce and their overlap against CTA caps and reserved SMs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.aux:
+    if args.comm_probe:
+        run_comm_probe(args)
+    elif args.aux:
         run_aux(args)
     elif args.impl == "reference":
         run_reference(args)
