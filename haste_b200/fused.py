@@ -230,10 +230,11 @@ class ShardedFFILayer:
         slower with fewer CTAs and with more ranks (four B200s, 1.5 MB: 45 us with NCCL's default, 55 us with 16 CTAs, 82
         us with 8), the fused kernel gets slower with fewer SMs, and a kernel much longer than the collective loses more
         from missing SMs than it can win from the overlap.  Measured at 670K labels (per-step time, 8 / 12 / 16 SMs
-        reserved): four ranks 88 / 85 / 87 us, eight ranks 90 / 70 / 60 us; at 2.8M labels on four ranks 630 / - / 654 us."""
+        reserved): four ranks 88 / 85 / 87 us, eight ranks 90 / 70 / 60 us; at 2.8M labels four ranks 630 / - / 654 us, eight
+        ranks 347 / - / 353 us."""
         sh = self.shard
         est_kernel_ms = 6.0 * B * sh.L * sh.F / 500e12 * 1e3        # the fused kernel sustains about 500 TFLOP/s
-        if est_kernel_ms > 0.5 or self.world <= 2:
+        if est_kernel_ms > 0.2 or self.world <= 2:
             return 8
         return 12 if self.world <= 4 else 16
 
