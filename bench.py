@@ -421,6 +421,7 @@ def _c5_lines(args, rank, world, device, flush, dist):
     ms, _, _ = _time_steps(layer, dev_batches, steps, warmup, world, device, flush, dist)
     kern, kern_ranks = _time_kernel(layer.shard, dev_batches[0][0], dev_batches[0][1], device, flush, 5, dist, world)
     parity = _check_ranks_agree(layer, dev_batches[0][0], dev_batches[0][1], device, dist, world)
+    layer.close()
     del layer
     torch.cuda.empty_cache()
     out = {"value": c["B"] / (statistics.median(ms) * 1e-3), "unit": "samples/s", "ms_per_step": statistics.median(ms), "steps": steps,
@@ -809,12 +810,16 @@ def run_comm_probe(args):
         for name, pg in groups.items():
             emit(f"kernel ({free} SMs left free) beside the all-reduce, {name}", timed(lambda: both(pg)))
     del layer
+    for pg in groups.values():                        # communicators hold channels and buffers: one capped one at a time
+        if pg is not None:
+            dist.destroy_process_group(pg)
     for reserve, own in ((8, False), (8, True), (12, True), (16, True), (24, True)):
         layer = ShardedFFILayer(loc, W, bias, G, D, device, reserve_sms=reserve, **kw)
         if not own:
             layer._comm_ready = True                  # keep the caller's (default) communicator for the dX all-reduce
         ms, _, _ = _time_steps(layer, dev_batches, 60, 10, world, device, flush, dist)
         emit(f"pipelined step, {reserve} SMs reserved, " + ("capped communicator" if own else "default communicator"), statistics.median(ms) * 1e3)
+        layer.close()
         del layer
         torch.cuda.empty_cache()
     dist.barrier()
