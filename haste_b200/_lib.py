@@ -47,6 +47,7 @@ SIGNATURES = {
     "haste_ffi_rewire_prepared": [P, P, P, I64, I64, I64, I64, I64, I32, U32, I32, I32, I32, U64, U32, P, P, P],
     "haste_ffi_step": [P, P, I64, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I32, F32, F32, F32, F32, U64, U32, U32, P],
     "haste_topk_update": [P, I64, I64, I64, I64, I32, P, P, P],
+    "haste_ffi_topk": [P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, I32, I64, P, P, P],
     "haste_ffi_check_locations": [P, I64, I64, P],
     "haste_ffi_set_max_ctas": [I32],
     "haste_poll_status": [],

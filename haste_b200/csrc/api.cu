@@ -347,6 +347,32 @@ int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t 
   return launch_topk_update(z, ldz, B, C, col0, k, vals, idx, static_cast<cudaStream_t>(stream));
 }
 
+int haste_ffi_topk(const int32_t* loc, const void* xt, const void* w, const void* bias, void* zbuf, int64_t ldz, int64_t B, int64_t D,
+                   int64_t F, int64_t L, int64_t G, int64_t groups_per_chunk, int32_t k, int64_t label0, float* vals, int32_t* idx,
+                   haste_stream_t stream) {
+  const char* who = "haste_ffi_topk";
+  REQUIRE_PTR(loc, who); REQUIRE_PTR(xt, who); REQUIRE_PTR(w, who); REQUIRE_PTR(zbuf, who); REQUIRE_PTR(vals, who); REQUIRE_PTR(idx, who);
+  REQUIRE_ALIGNED(xt, who); REQUIRE_ALIGNED(w, who); REQUIRE_ALIGNED(zbuf, who);
+  if (int rc = validate_shape(who, B, D, F, L, G)) return rc;
+  if (k < 1 || k > 128) return fail(HASTE_ERR_UNSUPPORTED, "%s: k=%d outside [1,128]", who, k);
+  if (groups_per_chunk < 1 || label0 < 0) return fail(HASTE_ERR_BAD_ARG, "%s: bad chunk size or label offset", who);
+  if (ldz < groups_per_chunk * G || (ldz % 8) != 0)
+    return fail(HASTE_ERR_BAD_ARG, "%s: the logit buffer needs a row stride of at least groups_per_chunk * G columns, a multiple of 8", who);
+  if (label0 + L >= (1ll << 31)) return fail(HASTE_ERR_UNSUPPORTED, "%s: label ids must fit in int32", who);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t NG = (L + G - 1) / G;
+  const char* wb = static_cast<const char*>(w);
+  const char* bb = static_cast<const char*>(bias);
+  for (int64_t g0 = 0; g0 < NG; g0 += groups_per_chunk) {
+    const int64_t g1 = g0 + groups_per_chunk < NG ? g0 + groups_per_chunk : NG;
+    const int64_t l0 = g0 * G, l1 = g1 * G < L ? g1 * G : L, C = l1 - l0;
+    const int64_t zw = (C + 7) / 8 * 8;        // the forward writes zeros into the columns that pad the last group's row
+    if (int rc = launch_forward(loc + g0 * F, xt, wb + l0 * F * 2, bias ? bb + l0 * 2 : nullptr, zbuf, B, D, F, C, G, ldz, zw, st)) return rc;
+    if (int rc = launch_topk_update(zbuf, ldz, B, C, label0 + l0, k, vals, idx, st)) return rc;
+  }
+  return HASTE_OK;
+}
+
 int haste_ffi_check_locations(const int32_t* loc, int64_t n, int64_t D, haste_stream_t stream) {
   const char* who = "haste_ffi_check_locations";
   REQUIRE_PTR(loc, who);

@@ -289,6 +289,19 @@ def rewire_ex(w, loc, mom_w, D, G, group0, score_mode, prune_mode, threshold, n_
               "ffi_rewire_ex")
 
 
+def topk(loc, xt, w, bias, zbuf, groups_per_chunk, k, G, label0, vals, idx):
+    """Chunked forward + running top-k of the whole layer in one library call (``zbuf``: bf16 [B, >= groups_per_chunk * G])."""
+    _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)
+    _req(zbuf, "logit buffer", torch.bfloat16); _req(vals, "values", torch.float32); _req(idx, "labels", torch.int32)
+    if bias is not None:
+        _req(bias, "bias", torch.bfloat16)
+    D, B = xt.shape
+    L, F = w.shape
+    with torch.cuda.device(xt.device):
+        check(lib.haste_ffi_topk(_ptr(loc), _ptr(xt), _ptr(w), _ptr(bias), _ptr(zbuf), zbuf.stride(0), B, D, F, L, G, groups_per_chunk, k,
+                                 label0, _ptr(vals), _ptr(idx), _stream(xt)), "ffi_topk")
+
+
 def topk_update(z, C, col0, vals, idx):
     """Fold logits z[:, :C] (labels col0..col0+C-1) into the running top-k state (vals fp32 [B,k], idx int32 [B,k])."""
     _req(z, "logits", torch.bfloat16, contiguous=False); _req(vals, "vals", torch.float32); _req(idx, "idx", torch.int32)

@@ -33,9 +33,8 @@ def ffi_topk(group_locations, weights, bias, features, k, group_size, *, groups_
     xt = _ffi.transpose_bf16(features)
     vals = torch.full((B, k), float("-inf"), dtype=torch.float32, device=dev)
     idx = torch.full((B, k), -1, dtype=torch.int32, device=dev)
-    for g0 in range(0, NG, groups_per_chunk):
-        g1 = min(NG, g0 + groups_per_chunk)
-        l0, l1 = g0 * G, min(L, g1 * G)
-        z = _ffi.forward(group_locations[g0:g1], xt, weights[l0:l1], None if bias is None else bias[l0:l1], G)
-        _ffi.topk_update(z, l1 - l0, label0 + l0, vals, idx)
+    # one library call walks the chunks (forward kernel, then the running top-k kernel, per chunk) on the current stream
+    groups_per_chunk = min(int(groups_per_chunk), NG)
+    zbuf = torch.empty(B, groups_per_chunk * G, dtype=torch.bfloat16, device=dev)
+    _ffi.topk(group_locations, xt, weights, bias, zbuf, groups_per_chunk, k, G, label0, vals, idx)
     return vals, idx

@@ -292,6 +292,16 @@ int haste_ffi_step(const void* x, const int32_t* coo, int64_t nnz, const int32_t
 int haste_topk_update(const void* z, int64_t ldz, int64_t B, int64_t C, int64_t col0, int32_t k,
                       float* vals, int32_t* idx, haste_stream_t stream);
 
+/* The whole inference top-k in one call: the layer's labels are walked in chunks of `groups_per_chunk` label groups;
+ * each chunk's logits go to zbuf (bf16 [B, ldz], ldz >= groups_per_chunk * G, ldz % 8 == 0, 16-byte aligned; sized to
+ * stay in L2) through haste_ffi_forward's kernels and are folded into vals / idx by haste_topk_update's kernel, all on
+ * `stream` without returning to the host in between.  vals / idx as for haste_topk_update (start at -inf / -1);
+ * `label0` is added to the label ids (a shard of a larger layer).  Replaces forward + torch.topk over the full
+ * [B,L] logits (src/evaluate.py:151-156, 219). */
+int haste_ffi_topk(const int32_t* loc, const void* xt, const void* w, const void* bias, void* zbuf, int64_t ldz, int64_t B,
+                   int64_t D, int64_t F, int64_t L, int64_t G, int64_t groups_per_chunk, int32_t k, int64_t label0,
+                   float* vals, int32_t* idx, haste_stream_t stream);
+
 /* Rate probes (measurement only; timed by the benchmark's auxiliary mode; no counterpart in the reference).  Each
  * isolates one access pattern of the fused train step at the step's own sizes:
  *   haste_probe_red_rate     fp32 reduce-add of `tiles_per_cta` tiles of 64 rows x 128 floats per SM into dxt [D,B]
