@@ -53,6 +53,7 @@ SIGNATURES = {
     "haste_poll_status": [],
     "haste_debug_set_wait_limit": [c_longlong],
     "haste_debug_stall_next_step": [I32],
+    "haste_debug_set_dependent_launch": [I32],
     "haste_probe_red_rate": [P, I64, I64, I32, I32, P],
     "haste_probe_gather_rate": [P, I64, I64, I32, I32, P],
     "haste_probe_umma_rate": [I32, I32, I32, I32, P, P],

@@ -192,6 +192,9 @@ __global__ void __launch_bounds__(PREP_THREADS) step_prepare_kernel(const uint16
   extern __shared__ int32_t cnt[];          // NG counters, then reused as fill cursors
   __shared__ int part[PREP_THREADS];
   const int tid = threadIdx.x;
+  // the fused step that follows in the stream may place its CTAs and set up its shared memory and TMEM already (it
+  // waits for this grid to complete before it reads anything this kernel writes)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.x == 0) {
     // One block does the whole bucketing, so its two passes over the entries keep four independent 8-byte loads
     // in flight per thread (a batch of C5 has ~37 K entries; one load at a time costs one L2 latency per entry).

@@ -200,6 +200,9 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // Everything above touched only this CTA's shared memory and TMEM, so it may run while the preparation kernel that
+  // precedes the step in the stream is still finishing; from here on the step reads what that kernel wrote.
+  grid_dependency_wait();
 
   // Groups are dealt round-robin; the incomplete last round goes to the highest-numbered CTAs.  The head of a
   // long-tailed label distribution sits in the first groups, whose tiles are the expensive ones (positives, target
@@ -847,7 +850,15 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
     auto k = ffi_train_step_sm100_kernel<G_, F_, LK, WLOSS, MOMF, DBG>;                                             \
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);            \
     if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));         \
-    k<<<grid, C::NTHREADS, C::SMEM_BYTES, st>>>(a, u, tm_x, tm_w);                                                  \
+    cudaLaunchConfig_t cfg = {};                                                                                   \
+    cfg.gridDim = dim3(static_cast<unsigned>(grid)); cfg.blockDim = dim3(C::NTHREADS);                              \
+    cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = st;                                                          \
+    cudaLaunchAttribute attr[1];                                                                                    \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                                \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;   /* the prologue overlaps the preceding kernel's tail */ \
+    cfg.attrs = attr; cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;                                            \
+    e = cudaLaunchKernelEx(&cfg, k, a, u, tm_x, tm_w);                                                              \
+    if (e != cudaSuccess) return fail(HASTE_ERR_LAUNCH, "cudaLaunchKernelEx: %s", cudaGetErrorString(e));           \
   }
 #define HASTE_S100_BY_LOSS(WLOSS, MOMF, DBG)                                                                       \
   { if (loss_kind == HASTE_LOSS_BCE) HASTE_S100_LAUNCH(HASTE_LOSS_BCE, WLOSS, MOMF, DBG) else HASTE_S100_LAUNCH(HASTE_LOSS_SQHINGE, WLOSS, MOMF, DBG) }

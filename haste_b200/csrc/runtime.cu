@@ -15,6 +15,7 @@ static std::mutex g_mu;
 static int* g_status_host = nullptr;
 static long long g_wait_limit = 4000000000ll;   // clock cycles (~2 s)
 static int g_stall_tile = -1;                   // test hook: consumed by the next debug step
+static int g_dependent_launch = 1;              // the fused step is launched with programmatic stream serialization
 
 int device_status_word(int** dev_ptr) {
   std::lock_guard<std::mutex> lock(g_mu);
@@ -45,6 +46,7 @@ int report_pending_status(const char* who) {
 }
 
 long long wait_limit_cycles() { return g_wait_limit; }
+int dependent_launch_enabled() { return g_dependent_launch; }
 int take_stall_tile() {
   std::lock_guard<std::mutex> lock(g_mu);
   const int t = g_stall_tile;
@@ -95,6 +97,12 @@ int haste_debug_set_wait_limit(long long cycles) {
   if (cycles < 1000) return haste::fail(HASTE_ERR_BAD_ARG, "haste_debug_set_wait_limit: %lld cycles is too short", cycles);
   std::lock_guard<std::mutex> lock(haste::g_mu);
   haste::g_wait_limit = cycles;
+  return HASTE_OK;
+}
+
+int haste_debug_set_dependent_launch(int on) {
+  std::lock_guard<std::mutex> lock(haste::g_mu);
+  haste::g_dependent_launch = on ? 1 : 0;
   return HASTE_OK;
 }
 

@@ -13,6 +13,8 @@ int take_device_status();
 int report_pending_status(const char* who);
 // Clock cycles a device-side wait may last before it gives up.
 long long wait_limit_cycles();
+// 1 (default): the fused step may start its prologue while the preceding kernel of the stream finishes.
+int dependent_launch_enabled();
 // Test hook: tile index at which the next debug step withholds one barrier arrival (-1 = none); reading clears it.
 int take_stall_tile();
 

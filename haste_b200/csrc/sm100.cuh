@@ -274,6 +274,14 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn_major, 
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it in the stream is still running; grid_dependency_wait() returns once that kernel has
+// completed and its memory is visible, so everything before the call must not touch global memory the stream's
+// earlier work produces.  grid_launch_dependents() (in the earlier kernel) lets the next kernel's CTAs start
+// as soon as SMs are free instead of at this grid's end.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -198,6 +198,10 @@ int haste_poll_status(void);
  * traps, the kernel drains and returns. */
 int haste_debug_set_wait_limit(long long cycles);
 int haste_debug_stall_next_step(int32_t tile);
+/* The fused step is launched so that its set-up (barriers, shared memory, TMEM) may overlap the tail of the kernel
+ * before it in the stream (programmatic dependent launch; it waits for that kernel before it reads anything);
+ * haste_debug_set_dependent_launch(0) launches it the ordinary way (measurement of the difference). */
+int haste_debug_set_dependent_launch(int32_t on);
 
 /* Elementwise stochastic rounding fp32 -> bf16 with the reference stream over the flat index.
  * Replaces sr_triton.stochastic_rounding (shared_ffi/sr_triton.py:27-59). */
