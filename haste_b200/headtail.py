@@ -93,3 +93,69 @@ def penultimate_transposed(x, weight, bias=None, relu=True):
     if relu:
         xt = torch.relu_(xt)
     return xt.contiguous()
+
+
+class HeadTailFusedStep:
+    """One training step of the head/tail output layer with no [B, L] tensor in either part and no autograd graph:
+    the sparse tail runs the fused FFI step (forward, loss, both backward products and the SR-SGD update in one kernel,
+    ``FusedFFIShard``), the dense head — ``num_head`` frequent labels, a [B, num_head] problem — runs as library GEMMs
+    around an elementwise loss gradient, and its weights take the same SR-SGD update through ``haste_sgd_sr_update``.
+    The loss is separable over labels (BCE with logits summed, or the squared hinge), so the two parts only share the
+    COO target list — head labels are the global ids below ``num_head``, the shard is built with ``label0 = num_head``
+    and drops them, as it drops the tail labels of other shards — and the scalar loss.
+
+    Counterpart in the reference: ``head_layer`` / ``tail_layer`` evaluated separately, ``torch.cat`` of the logits, one
+    loss over [B, L] and autograd back through the concatenation (src/model.py:182-197, 245-248; src/runner.py:469-483).
+    """
+
+    def __init__(self, head_weight, head_bias, tail_shard, *, momentum_head=None):
+        if tail_shard.label0 != head_weight.shape[0]:
+            raise ValueError("the tail shard's label0 must equal the number of head labels")
+        self.hw, self.hb, self.tail = head_weight, head_bias, tail_shard
+        self.num_head = head_weight.shape[0]
+        self.mom_hw = momentum_head
+
+    def _head_targets(self, targets, B):
+        y = torch.zeros(B, self.num_head, dtype=torch.bool, device=targets.device)
+        t = targets[targets[:, 1] < self.num_head].long()
+        y[t[:, 0], t[:, 1]] = True
+        return y
+
+    @torch.no_grad()
+    def step(self, head_x, tail_x, targets, want_loss=True):
+        """``head_x`` [B, Dh], ``tail_x`` [B, D] (bf16), ``targets`` int32 [nnz, 2] (row, global label id).  Returns
+        (d_head_x fp32 [B, Dh], dxt_tail fp32 [D, B], loss fp32 scalar tensor or None); weights, biases and momentum are
+        updated in place."""
+        sh = self.tail
+        B = head_x.shape[0]
+        seed, step_no = sh._keys()                     # this step's random-stream keys, shared by both parts
+        # ---- tail: one preparation launch + the fused kernel
+        dxt_tail, loss_tail = sh.step(tail_x, targets, want_loss=want_loss)
+        # ---- head: logits rounded to bf16 as the reference's are, gradient in fp32, rounded to bf16 for the products
+        z = torch.nn.functional.linear(head_x, self.hw, self.hb).float()
+        y = self._head_targets(targets, B)
+        gs = sh.grad_scale
+        if sh.loss_kind == _lib_loss("bce"):
+            g = (torch.sigmoid(z) - y.float()) * gs
+            loss_head = (torch.nn.functional.softplus(z) - torch.where(y, z, torch.zeros_like(z))).sum() * gs if want_loss else None
+        else:
+            s = torch.where(y, 1.0, -1.0)
+            m = torch.clamp_min(1.0 - s * z, 0.0)
+            g = -2.0 * gs * s * m
+            loss_head = (m * m).sum() * gs if want_loss else None
+        g = g.to(torch.bfloat16)
+        d_head_x = g.float() @ self.hw.float()
+        d_hw = (g.float().t() @ head_x.float()).to(torch.bfloat16)
+        flags = _ffi.make_flags(sr=sh.sr, contract=sh.contract, rng=sh.rng)
+        # head rows are global labels 0 .. num_head-1: row0 = 0 keeps their random bits disjoint from the tail's
+        _ffi.sgd_sr_update(self.hw, d_hw, self.mom_hw, 0, sh.lr, sh.wd, sh.mu if self.mom_hw is not None else 0.0, seed, step_no, flags)
+        if self.hb is not None:
+            d_hb = g.float().sum(0).to(torch.bfloat16)
+            _ffi.sgd_sr_update(self.hb.view(-1, 1), d_hb.view(-1, 1), None, 0, sh.lr, sh.wd, 0.0, seed ^ 0x62696173, step_no, flags)
+        loss = (loss_tail.reshape(()) + loss_head) if want_loss else None
+        return d_head_x, dxt_tail, loss
+
+
+def _lib_loss(name):
+    from .fused import LOSSES
+    return LOSSES[name]
