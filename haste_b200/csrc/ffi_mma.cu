@@ -1,8 +1,9 @@
 // Grouped fixed-fan-in GEMM kernels on warp-level mma (m16n8k16 bf16, fp32 accumulate).
 //
-// These kernels serve the unfused autograd surface (forward / backward-features /
-// backward-weights write their [B,L]-sized results to memory, so they are HBM-bound) and every
-// (G,F,B) shape.  One device routine, warp_gemm_tn, serves all three products because the three
+// These kernels serve every (G,F,B) shape: the forward, the backward entry points and the fused
+// step of the two benchmark layer shapes dispatch to the tcgen05 kernels, everything else (other
+// group sizes and fan-ins, batch sizes that are not multiples of 8, misaligned bases) runs here.
+// One device routine, warp_gemm_tn, serves all three products because the three
 // shared-memory tiles of a group can each play two roles without being transposed:
 //     Xs [F][BT]  gathered rows of xt (batch contiguous)
 //     Ws [G][F]   the group's weight rows
@@ -14,8 +15,6 @@
 // Bm stored n-major rows (kk contiguous).
 #include "common.cuh"
 #include "launchers.h"
-#include <stdlib.h>
-#include <string.h>
 
 namespace haste {
 
