@@ -263,3 +263,22 @@ def test_two_rank_gloo_layerwide_selection(tmp_path):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     for p, o in zip(procs, outs):
         assert p.returncode == 0 and "ok" in o, o
+
+
+def test_pipeline_reserve_choice(built_lib):
+    """SMs the pipelined multi-GPU step leaves to the collective: 8 for two ranks, 12 for up to four, 16 beyond, and 8
+    whenever the fused kernel is long against the all-reduce (the rule's figures are measured, see the docstring)."""
+    from haste_b200.fused import ShardedFFILayer
+
+    class _Shard:                      # the rule only looks at the shard's label count and fan-in
+        def __init__(self, L, F):
+            self.L, self.F = L, F
+
+    def choice(world, B, L_total, F):
+        layer = ShardedFFILayer.__new__(ShardedFFILayer)
+        layer.world, layer.shard = world, _Shard(L_total // world, F)
+        return layer._choose_reserve(B)
+
+    assert [choice(n, 512, 670091, 64) for n in (2, 4, 8)] == [8, 12, 16]           # 670K labels, B=512
+    assert [choice(n, 1024, 2812281, 64) for n in (2, 4, 8)] == [8, 8, 8]           # 2.8M labels, B=1024: long kernels
+    assert choice(16, 512, 670091, 64) == 16
