@@ -162,6 +162,24 @@ def step_prepare(x, xt, dxt, loss, coo, label0, L, G, tgt_ptr, tgt_ent):
                                          _ptr(tgt_ent), B, D, _stream(x)), "ffi_step_prepare")
 
 
+def step_prepare_on(stream_handle, x, xt, dxt, loss, coo, label0, L, G, tgt_ptr, tgt_ent):
+    """``step_prepare`` on an explicit stream (a ``cudaStream_t`` as int) with the tensors' device current: the
+    per-step path of the pipelined multi-GPU step, where dtype / contiguity are checked once by the caller."""
+    B, D = x.shape
+    check(lib.haste_ffi_step_prepare(x.data_ptr(), xt.data_ptr(), dxt.data_ptr(), loss.data_ptr(), coo.data_ptr(), coo.shape[0], label0, L, G,
+                                     tgt_ptr.data_ptr(), tgt_ent.data_ptr(), B, D, stream_handle), "ffi_step_prepare")
+
+
+def train_step_on(stream_handle, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, mu,
+                  seed, step, flags):
+    """``train_step`` on an explicit stream with the tensors' device current (see ``step_prepare_on``)."""
+    D, B = xt.shape
+    L, F = w.shape
+    check(lib.haste_ffi_train_step(loc.data_ptr(), xt.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(mom_w), _ptr(mom_b), tgt_ptr.data_ptr(),
+                                   tgt_ent.data_ptr(), dxt.data_ptr(), _ptr(loss), B, D, F, L, G, label0, loss_kind, grad_scale, lr, wd, mu,
+                                   seed, step, flags, stream_handle), "ffi_train_step")
+
+
 def train_step(loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, G, label0, loss_kind, grad_scale, lr, wd, mu,
                seed, step, flags):
     _req(loc, "locations", torch.int32); _req(xt, "features", torch.bfloat16); _req(w, "weights", torch.bfloat16)

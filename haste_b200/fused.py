@@ -282,9 +282,11 @@ class ShardedFFILayer:
         sh, b = self.shard, self._slots[slot]
         if targets.shape[0] > b["ent"].numel():
             b["ent"] = torch.zeros(int(targets.shape[0] * 1.5) + 1, dtype=torch.int32, device=targets.device)
-        with torch.cuda.stream(stream):
-            _ffi.step_prepare(x, b["xt"], b["dxt"], b["loss"], targets, sh.label0, sh.L, sh.G, b["ptr"], b["ent"])
-            b["prepared"].record(stream)
+        if x.dtype is not torch.bfloat16 or targets.dtype is not torch.int32 or not x.is_contiguous() or not targets.is_contiguous() \
+                or not x.is_cuda or not targets.is_cuda:
+            raise RuntimeError("step_pipelined: features must be a contiguous CUDA bf16 [B,D] tensor, targets a contiguous CUDA int32 [nnz,2] tensor")
+        _ffi.step_prepare_on(stream.cuda_stream, x, b["xt"], b["dxt"], b["loss"], targets, sh.label0, sh.L, sh.G, b["ptr"], b["ent"])
+        b["prepared"].record(stream)
 
     def step_pipelined(self, x, targets, next_batch=None, want_loss=True):
         """One step of the three-stream pipeline (see the class docstring).  ``next_batch``: (x, targets) of the
@@ -292,6 +294,9 @@ class ShardedFFILayer:
         part as a device scalar)."""
         sh = self.shard
         dev = x.device
+        if dev.index is not None and torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):              # the library calls below take the current device
+                return self.step_pipelined(x, targets, next_batch, want_loss)
         cur = torch.cuda.current_stream(dev)
         B, D = x.shape
         if self._slots is None or self._slots[0]["xt"].shape != (D, B):
@@ -311,8 +316,8 @@ class ShardedFFILayer:
         cur.wait_event(b["prepared"])
         seed, step = sh._keys()
         flags = _ffi.make_flags(sr=sh.sr, contract=sh.contract, rng=sh.rng, zero_dxt=False, loss=want_loss)
-        _ffi.train_step(sh.loc, b["xt"], sh.w, sh.bias, sh.mom_w, sh.mom_b, b["ptr"], b["ent"], b["dxt"], b["loss"] if want_loss else None,
-                        sh.G, sh.label0, sh.loss_kind, sh.grad_scale, sh.lr, sh.wd, sh.mu, seed, step, flags)
+        _ffi.train_step_on(cur.cuda_stream, sh.loc, b["xt"], sh.w, sh.bias, sh.mom_w, sh.mom_b, b["ptr"], b["ent"], b["dxt"],
+                           b["loss"] if want_loss else None, sh.G, sh.label0, sh.loss_kind, sh.grad_scale, sh.lr, sh.wd, sh.mu, seed, step, flags)
         sh.steps += 1
         # (2) the previous step's all-reduce, beside this step's kernel (after the kernel that made its input)
         if prev is not None and self.world > 1:
