@@ -3,7 +3,7 @@
 // thread-local message.
 #include "common.cuh"
 #include "launchers.h"
-
+#include "runtime.h"
 
 namespace haste {
 
@@ -224,8 +224,12 @@ int haste_ffi_step(const void* x, const int32_t* coo, int64_t nnz, const int32_t
                    int64_t G, int64_t label0, int32_t loss_kind, float grad_scale, float lr, float wd, float mu, uint64_t seed,
                    uint32_t step, uint32_t flags, haste_stream_t stream) {
   if (int rc = haste_ffi_step_prepare(x, xt, dxt, loss, coo, nnz, label0, L, G, tgt_ptr, tgt_ent, B, D, stream)) return rc;
-  return train_step_impl(nullptr, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, B, D, F, L, G, label0, loss_kind, grad_scale,
-                         lr, wd, mu, seed, step, flags & ~static_cast<uint32_t>(HASTE_F_ZERO_DXT), stream);
+  // the step follows its own preparation kernel in the same stream: its set-up may overlap that kernel's tail
+  dependent_launch_scope(1);
+  const int rc = train_step_impl(nullptr, loc, xt, w, bias, mom_w, mom_b, tgt_ptr, tgt_ent, dxt, loss, B, D, F, L, G, label0, loss_kind,
+                                 grad_scale, lr, wd, mu, seed, step, flags & ~static_cast<uint32_t>(HASTE_F_ZERO_DXT), stream);
+  dependent_launch_scope(0);
+  return rc;
 }
 
 int haste_ffi_train_step_dbg(const int32_t* loc, const void* xt, void* w, void* bias, float* mom_w, float* mom_b, const int32_t* tgt_ptr,

@@ -46,7 +46,13 @@ int report_pending_status(const char* who) {
 }
 
 long long wait_limit_cycles() { return g_wait_limit; }
-int dependent_launch_enabled() { return g_dependent_launch; }
+// The relaxed launch is only used where this library knows what precedes the step in the stream: inside haste_ffi_step,
+// right behind its own preparation kernel.  (Behind an event wait on another stream — the pipelined multi-GPU step
+// waits for a preparation kernel of a side stream — the relaxed edge would only cover the previous kernel of the
+// same stream, and the step could read the batch before it is prepared.)
+static thread_local int t_dependent_scope = 0;
+void dependent_launch_scope(int on) { t_dependent_scope = on; }
+int dependent_launch_enabled() { return g_dependent_launch && t_dependent_scope; }
 int take_stall_tile() {
   std::lock_guard<std::mutex> lock(g_mu);
   const int t = g_stall_tile;

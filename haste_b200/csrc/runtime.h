@@ -13,8 +13,10 @@ int take_device_status();
 int report_pending_status(const char* who);
 // Clock cycles a device-side wait may last before it gives up.
 long long wait_limit_cycles();
-// 1 (default): the fused step may start its prologue while the preceding kernel of the stream finishes.
+// 1: the fused step about to be launched by this thread may start its set-up while the preceding kernel of the
+// stream finishes (only inside dependent_launch_scope(1), and unless switched off for measurement).
 int dependent_launch_enabled();
+void dependent_launch_scope(int on);
 // Test hook: tile index at which the next debug step withholds one barrier arrival (-1 = none); reading clears it.
 int take_stall_tile();
 

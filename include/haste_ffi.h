@@ -198,9 +198,10 @@ int haste_poll_status(void);
  * traps, the kernel drains and returns. */
 int haste_debug_set_wait_limit(long long cycles);
 int haste_debug_stall_next_step(int32_t tile);
-/* The fused step is launched so that its set-up (barriers, shared memory, TMEM) may overlap the tail of the kernel
- * before it in the stream (programmatic dependent launch; it waits for that kernel before it reads anything);
- * haste_debug_set_dependent_launch(0) launches it the ordinary way (measurement of the difference). */
+/* Inside haste_ffi_step the fused step is launched so that its set-up (barriers, shared memory, TMEM) may overlap
+ * the tail of the preparation kernel before it (programmatic dependent launch; it waits for that kernel before it
+ * reads anything); haste_debug_set_dependent_launch(0) launches it the ordinary way (measurement of the
+ * difference).  haste_ffi_train_step on its own is always launched the ordinary way. */
 int haste_debug_set_dependent_launch(int32_t on);
 
 /* Elementwise stochastic rounding fp32 -> bf16 with the reference stream over the flat index.

@@ -161,11 +161,14 @@ def test_sm100_backward_both(hb, shape):
 
 @pytest.mark.parametrize("loss", ["squared_hinge", "bce"])
 def test_sm100_step_rank_count_independent(hb, loss):
-    """A layer split over ranks (contiguous group ranges of equal estimated cost) must give bit-identical weights
-    and bias to the unsplit layer — random bits are drawn by global label — and the same dX up to the fp32
-    summation order.  The ranks are run one after the other on this GPU; their dX are added on the host."""
+    """A layer split over ranks (contiguous group ranges) must give bit-identical weights and bias to the unsplit
+    layer — random bits are drawn by global label, and the order in which a group's batch tiles enter its dW accumulator
+    is a function of the global group index — and the same dX up to the fp32 summation order.  The ranks are run one
+    after the other on this GPU; their dX are added on the host.  Splits: by estimated cost, and at explicit odd and
+    even group boundaries (a rotation of the tile order by anything local — CTA index, shard-local group index —
+    shows up as a few differing weights when a shard starts at a group index that is not a multiple of the tile count)."""
     from haste_b200.fused import FusedFFIShard, group_cost_from_targets, split_groups_by_cost
-    B, D, L = 256, 256, 128 * 37 + 50
+    B, D, L = 384, 256, 128 * 37 + 50                          # three batch tiles
     inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=11, bias_zero=False)
     X, coo = inp["X"].cuda(), inp["targets"].cuda()
     kw = dict(loss=loss, lr=0.05, weight_decay=1e-4, seed=123, rng="packed", grad_scale=0.5)
@@ -182,14 +185,14 @@ def test_sm100_step_rank_count_independent(hb, loss):
     NG = (L + G - 1) // G
     w_all, b_all, dxt_all, loss_all = run(0, NG)
     cost = group_cost_from_targets(inp["targets"], L, G, B)
-    bounds = split_groups_by_cost(cost, 3)
-    assert bounds[0] == 0 and bounds[-1] == NG
-    parts = [run(bounds[r], bounds[r + 1]) for r in range(3)]
-    assert np.array_equal(_bits(torch.cat([p[0] for p in parts])), _bits(w_all))
-    assert np.array_equal(_bits(torch.cat([p[1] for p in parts])), _bits(b_all))
-    dxt_sum = sum(p[2] for p in parts)
-    _close(dxt_sum, dxt_all, 1e-4, 1e-5 * float(dxt_all.abs().max()), "dX summed over ranks")
-    assert abs(sum(p[3] for p in parts) - loss_all) <= 1e-4 * abs(loss_all) + 1e-6
+    for bounds in (split_groups_by_cost(cost, 3), [0, 9, NG], [0, 14, NG], [0, 5, 19, 20, NG], [0, 1, 2, NG]):
+        assert bounds[0] == 0 and bounds[-1] == NG
+        parts = [run(bounds[r], bounds[r + 1]) for r in range(len(bounds) - 1)]
+        assert np.array_equal(_bits(torch.cat([p[0] for p in parts])), _bits(w_all)), bounds
+        assert np.array_equal(_bits(torch.cat([p[1] for p in parts])), _bits(b_all)), bounds
+        dxt_sum = sum(p[2] for p in parts)
+        _close(dxt_sum, dxt_all, 1e-4, 1e-5 * float(dxt_all.abs().max()), "dX summed over ranks")
+        assert abs(sum(p[3] for p in parts) - loss_all) <= 1e-4 * abs(loss_all) + 1e-6
 
 
 @pytest.mark.parametrize("kind", KINDS, ids=["G128F64", "G64F128"])
