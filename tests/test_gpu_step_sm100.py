@@ -168,7 +168,7 @@ def test_sm100_step_rank_count_independent(hb, loss):
     even group boundaries (a rotation of the tile order by anything local — CTA index, shard-local group index —
     shows up as a few differing weights when a shard starts at a group index that is not a multiple of the tile count)."""
     from haste_b200.fused import FusedFFIShard, group_cost_from_targets, split_groups_by_cost
-    B, D, L = 384, 256, 128 * 37 + 50                          # three batch tiles
+    B, D, L = 512, 256, 128 * 37 + 50                          # four batch tiles: the tile order is rotated with period 4
     inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=11, bias_zero=False)
     X, coo = inp["X"].cuda(), inp["targets"].cuda()
     kw = dict(loss=loss, lr=0.05, weight_decay=1e-4, seed=123, rng="packed", grad_scale=0.5)
