@@ -160,18 +160,12 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = static_cast<int>((a.B + BT - 1) / BT);
-  // A group's batch tiles are walked in a rotated order, so that, at any moment, the dX reductions of different SMs —
-  // which work on neighbouring groups — are spread over the dxt array instead of all landing in the same 128 batch
-  // columns.  The rotation is (the group's GLOBAL index modulo R) * T / R with R = gcd(T, 4): global (this shard's first
-  // label / G + the local index), because the order in which a group's tiles enter its dW accumulator, and with it
-  // the last bit of the fp32 sum, must not depend on the rank or CTA the group lands on (a shard boundary at an odd
-  // group index showed 3 of 306,304 weights differing from the unsharded run while the rotation was by CTA index).
-  // The grid is a multiple of R and the incomplete last round is dealt accordingly (see below), so every group of a
-  // CTA has the same index modulo R and the rotation is one constant per CTA (a per-group value measured 4 % slower at
-  // 670K labels); R stops at 4 so that the usual grid sizes — 148, or 140 / 136 / 132 beside a collective — lose no SM.
-  const int R = (T % 4 == 0) ? 4 : ((T % 2 == 0) ? 2 : 1);
-  const int rot = static_cast<int>((u.label0 / G + static_cast<int64_t>(blockIdx.x)) % R) * (T / R);
-  auto tile_b0 = [&](int t) { int tt = t + rot; if (tt >= T) tt -= T; return tt * BT; };
+  // Every group's batch tiles are walked in the same order, t = 0 .. T-1: the order in which the tiles enter a group's
+  // dW accumulator — and with it the last bit of the fp32 sum — must not depend on the rank or CTA the group lands on.
+  // (An earlier build rotated the order by CTA index to spread the dX reductions of neighbouring SMs over dxt; a shard
+  // boundary at an odd group index then showed 3 of 306,304 weights differing from the unsharded run.  Rotations by
+  // the global group index with period 2, 4 or 8 all measured within 1 % of no rotation, which is what is left.)
+  auto tile_b0 = [&](int t) { return t * BT; };
   const bool has_bias = u.bias != nullptr;
 
   // ---------------- one-time setup
@@ -214,15 +208,11 @@ ffi_train_step_sm100_kernel(StepArgs a, UpdateArgs u, const __grid_constant__ CU
 
   // Groups are dealt round-robin; the incomplete last round goes to the highest-numbered CTAs.  The head of a
   // long-tailed label distribution sits in the first groups, whose tiles are the expensive ones (positives, target
-  // bitmap): the CTAs that own them then have one group less to do.  The grid size is a multiple of R (or the grid has
-  // one group per CTA), and the last round starts at a CTA index that is one too, so that CTA c only ever gets groups
-  // whose local index is congruent to c modulo R.
+  // bitmap): the CTAs that own them then have one group less to do.
   const int n_cta = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   const int full_rounds = a.NG / n_cta, rem_groups = a.NG - full_rounds * n_cta;
-  const int rem_up = (rem_groups + R - 1) / R * R;                 // <= n_cta: n_cta is a multiple of R whenever rem_groups > 0
-  const int last_r = cta - (n_cta - rem_up);                       // index inside the last round, if any
-  const int n_my_groups = full_rounds + ((last_r >= 0 && last_r < rem_groups) ? 1 : 0);
-  auto group_of = [&](int gi) { return gi < full_rounds ? cta + gi * n_cta : full_rounds * n_cta + last_r; };
+  const int n_my_groups = full_rounds + (cta >= n_cta - rem_groups ? 1 : 0);
+  auto group_of = [&](int gi) { return gi < full_rounds ? cta + gi * n_cta : full_rounds * n_cta + (cta - (n_cta - rem_groups)); };
 
   const int prod_id = warp == 0 ? 0 : (warp == 2 ? 1 : (warp >= C::W_XP ? 2 + warp - C::W_XP : -1));
   if (prod_id >= 0 && prod_id < C::NPW) {
@@ -856,12 +846,7 @@ int launch_step_shape(const int32_t* loc, const void* xt, const int32_t* tgt_ptr
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  // one CTA per SM, rounded down to a multiple of the rotation period R = gcd(batch tiles, 4) (the kernel's tile rotation
-  // relies on it); a layer with fewer groups than that gets one group per CTA
-  int grid = a.NG < sms ? a.NG : sms;
-  const int T = static_cast<int>((B + C::BT - 1) / C::BT);
-  const int R = (T % 4 == 0) ? 4 : ((T % 2 == 0) ? 2 : 1);
-  if (grid >= R) grid -= grid % R;
+  const int grid = a.NG < sms ? a.NG : sms;
   const bool wl = (u.flags & HASTE_F_LOSS) && loss != nullptr;
   const bool mom = u.mom_w != nullptr;
 #define HASTE_S100_LAUNCH(LK, WLOSS, MOMF, DBG)                                                                     \

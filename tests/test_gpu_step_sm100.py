@@ -163,12 +163,12 @@ def test_sm100_backward_both(hb, shape):
 def test_sm100_step_rank_count_independent(hb, loss):
     """A layer split over ranks (contiguous group ranges) must give bit-identical weights and bias to the unsplit
     layer — random bits are drawn by global label, and the order in which a group's batch tiles enter its dW accumulator
-    is a function of the global group index — and the same dX up to the fp32 summation order.  The ranks are run one
+    does not depend on where the group runs — and the same dX up to the fp32 summation order.  The ranks are run one
     after the other on this GPU; their dX are added on the host.  Splits: by estimated cost, and at explicit odd and
     even group boundaries (a rotation of the tile order by anything local — CTA index, shard-local group index —
     shows up as a few differing weights when a shard starts at a group index that is not a multiple of the tile count)."""
     from haste_b200.fused import FusedFFIShard, group_cost_from_targets, split_groups_by_cost
-    B, D, L = 512, 256, 128 * 37 + 50                          # four batch tiles: the tile order is rotated with period 4
+    B, D, L = 512, 256, 128 * 37 + 50                          # four batch tiles
     inp = fo.make_inputs(B, D, L, F, G, 6, 1.1, seed=11, bias_zero=False)
     X, coo = inp["X"].cuda(), inp["targets"].cuda()
     kw = dict(loss=loss, lr=0.05, weight_decay=1e-4, seed=123, rng="packed", grad_scale=0.5)
